@@ -210,19 +210,23 @@ class CacheManager:
         rc.n_tokens = n_tokens
 
     def trim(self, rid: Hashable) -> int:
-        """Give back the pages of window groups that no later token can read.
-        The next query sits at position n_tokens and reads keys from
-        n_tokens - window + 1 on.  Returns the number of pages freed."""
+        """Give back the pages that no later token can read.  The next query sits at position n_tokens.  Under a
+        window it reads keys from n_tokens - window + 1 on, and the first ``keep_first`` positions, whose pages stay;
+        under chunks it reads keys from the start of its own chunk on.  Returns the number of pages freed."""
         rc = self.requests[rid]
         freed = 0
         for g in self.groups:
-            if g.need.window is None:
+            if g.need.window is not None:
+                first_pos = rc.n_tokens - g.need.window + 1
+            elif g.need.chunk is not None:
+                first_pos = rc.n_tokens - rc.n_tokens % g.need.chunk
+            else:
                 continue
-            first_pos = rc.n_tokens - g.need.window + 1
             if first_pos <= 0:
                 continue
             table = rc.tables[g.gid]
-            for i in range(min(first_pos // self.page_size, len(table))):
+            kept_pages = _ceil_div(g.need.keep_first, self.page_size) if g.need.window is not None else 0
+            for i in range(kept_pages, min(first_pos // self.page_size, len(table))):
                 if table[i] >= 0:
                     g.allocator.free([table[i]])
                     table[i] = -1

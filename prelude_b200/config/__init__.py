@@ -4,9 +4,11 @@ from .registry import (ConfigError, load_model_config, load_model_spec, read_con
 from . import qwen3 as _qwen3  # noqa: F401  (registers Qwen3)
 from . import pabelix as _pabelix  # noqa: F401  (registers Pabelix)
 from . import kolisun as _kolisun  # noqa: F401  (registers Kolisun)
+from . import nedesun as _nedesun  # noqa: F401  (registers Nedesun)
 from .kolisun import KolisunConfig
+from .nedesun import NedesunConfig
 from .pabelix import PabelixConfig
 from .qwen3 import Qwen3Config
 
-__all__ = ["ConfigError", "Qwen3Config", "PabelixConfig", "KolisunConfig", "load_model_config", "load_model_spec", "read_config_json",
+__all__ = ["ConfigError", "Qwen3Config", "PabelixConfig", "KolisunConfig", "NedesunConfig", "load_model_config", "load_model_spec", "read_config_json",
            "register_architecture", "registered_architectures", "resolve_architecture", "unregister_architecture"]

@@ -222,12 +222,123 @@ class StateSpaceSpec:
 
 
 @dataclass(frozen=True)
+class ValueBlendSpec:
+    """Values blended across layers: the first layer of a model that names ``key`` keeps its values of the step's
+    tokens (``source``); every later layer with the same key replaces its own values by
+    (1 - lambda) v + lambda v_source, lambda a learned number (``name``), before they are cached."""
+    key: str
+    source: bool
+    name: str = "vmix"
+
+
+@dataclass(frozen=True)
+class MaskedAttentionSpec:
+    """Grouped-query softmax attention over a paged cache whose options are per head: an RMS norm of every q head and
+    every k head over its own elements with one scale shared by all heads (``head_norm_eps``), a rotation of the
+    first ``position.dims`` elements of every head (or none), and one of two masks.  ``window``: position i sees j
+    with 0 <= i - j < window, and also every j < ``keep_first``.  ``chunk``: i sees j <= i only inside its own run
+    of ``chunk`` positions, counted from position 0.  ``softcap``: score <- softcap * tanh(score / softcap) after
+    the scale.  ``sink``: a learned number per head joins the softmax's denominator.  ``head_gate``: head h's output
+    is multiplied by sigmoid((W_gate x)_h).  ``value_blend``: see ``ValueBlendSpec``.  Biases on q, k, v
+    (``qkv_bias``) and on the output projection (``o_bias``) are ``<name><bias_suffix>``."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    softmax_scale: float
+    position: object                       # RotaryRatesSpec | NoPositionSpec
+    qkv_bias: bool = False
+    o_bias: bool = False
+    head_norm_eps: Optional[float] = None
+    window: Optional[int] = None
+    keep_first: int = 0
+    chunk: Optional[int] = None
+    softcap: Optional[float] = None
+    sink: bool = False
+    head_gate: bool = False
+    value_blend: Optional[ValueBlendSpec] = None
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+    gate_name: str = "g"
+    sink_name: str = "sink"
+    bias_suffix: str = ".b"
+    norm_suffix: str = ".norm"
+    kind: str = "masked_attention"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule.  q and k are ``num_kv_heads`` x ``head_dim``, v is ``num_heads`` x ``value_dim``; each
+    passes a causal convolution per channel over ``conv_taps`` tokens (last tap: the current token, no bias) and
+    SiLU; q and k become unit vectors per head (x / sqrt(sum x^2 + ``unit_eps``)), q times head_dim^(-1/2).
+    beta = sigmoid(W_b x), g = exp(-exp(A_log) softplus(W_a x + dt_bias)), one of each per head.  Per head (its q/k
+    head: h // (heads / kv heads)) the state S [head_dim, value_dim] moves as S <- g S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q.  o is brought to unit root mean square per head (``norm_eps``), scaled by a weight
+    over value_dim that the heads share, multiplied by silu(W_g x), and projected out.  The state (float32) and
+    the convolutions' last ``conv_taps`` - 1 inputs are carried per sequence."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    conv_suffix: str = ".conv"
+    beta_name: str = "b"
+    a_name: str = "a"
+    a_log_name: str = "A_log"
+    dt_bias_name: str = "dt_bias"
+    gate_name: str = "g"
+    norm_name: str = "norm"
+    o_name: str = "o"
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class WkvSpec:
+    """Time mixing with a decaying matrix state per head.  With x' the previous token's input (zeros before the
+    first), each of r, k, v, g, w reads its own blend x + (x' - x) mu_s.  r, k, v are projections of their blends
+    (``num_heads`` x ``head_dim``), the gate is silu(W_g blend_g), the decay w = exp(-exp(W_w2 tanh(W_w1 blend_w) + w0))
+    per head and key channel (``decay_rank``: rows of W_w1).  Per head o_t = (S + diag(u) k_t v_t^T)^T r_t, then
+    S <- diag(w_t) S + k_t v_t^T.  o is brought to unit root mean square per head (``norm_eps``), times a weight
+    over all heads' channels, times the gate, and projected out.  The state (float32) and the previous token's
+    input are carried per sequence."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    decay_rank: Optional[int]          # None: the decay's matrices give it by their shapes
+    norm_eps: float
+    mix_prefix: str = "mu."
+    r_name: str = "r"
+    k_name: str = "k"
+    v_name: str = "v"
+    gate_name: str = "g"
+    w1_name: str = "w1"
+    w2_name: str = "w2"
+    w0_name: str = "w0"
+    bonus_name: str = "u"
+    norm_name: str = "norm"
+    o_name: str = "o"
+    kind: str = "wkv"
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec:
     """Several mixers side by side on the same input; the result is the sum of their outputs, each times its
-    scale.  ``names[i]`` is mixer i's prefix below this mixer's."""
+    scale.  ``names[i]`` is mixer i's prefix below this mixer's.  With ``member_norms`` every member's output is
+    first brought to unit root mean square over the model width and multiplied by a learned weight
+    (``<prefix>.<names[i]><member_norms[i].suffix>``)."""
     mixers: Tuple[object, ...]
     scales: Tuple[float, ...]
     names: Tuple[str, ...]
+    member_norms: Optional[Tuple[NormSpec, ...]] = None
     kind: str = "parallel"
 
 
@@ -304,6 +415,9 @@ class BlockSpec:
     ff_post_norm: Optional[NormSpec] = None
     mixer_post_norm_name: str = "post_mixer_norm"
     ff_post_norm_name: str = "post_ff_norm"
+    # kind "prenorm_residual" only: every sublayer's output is multiplied by this before it joins the stream; there
+    # too ``feed_forward`` (with ``ff_norm``) may be None
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -313,6 +427,16 @@ class TokenEmbeddingSpec:
     hidden_size: int
     name: str = "model.embed_tokens.weight"
     kind: str = "token_embedding"
+
+
+@dataclass(frozen=True)
+class ScaledEmbeddingSpec:
+    """The token's row of the table times ``scale``; a tied head takes the table itself, without the scale."""
+    vocab_size: int
+    hidden_size: int
+    scale: float
+    name: str = "model.embed_tokens.weight"
+    kind: str = "token_embedding_scaled"
 
 
 @dataclass(frozen=True)

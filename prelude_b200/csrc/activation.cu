@@ -92,3 +92,21 @@ PB_API int pb_clamped_glu(const void* gate_up, void* out, int dtype, int n_token
     PB_CHECK_LAUNCH("clamped_glu");
     return 0;
 }
+
+
+// tanh, element by element in float32 (the squashing between the two small products of a learned decay).
+template <typename T>
+__global__ void tanh_kernel(const T* __restrict__ x, T* __restrict__ out, long long n) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) pb_st(out + i, tanhf(pb_ld(x + i)));
+}
+
+PB_API int pb_tanh(const void* x, void* out, int dtype, long long n, cudaStream_t stream) {
+    PB_REQUIRE(n >= 0 && x && out, "tanh: bad arguments");
+    if (n == 0) return 0;
+    PB_DISPATCH_DTYPE(dtype, T, (pb_launch(tanh_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const T*)x, (T*)out, n)));
+    PB_CHECK_LAUNCH("tanh");
+    return 0;
+}

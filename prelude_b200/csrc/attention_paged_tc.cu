@@ -1,7 +1,8 @@
 // Paged softmax attention on the tensor cores (bfloat16 operands, float32 sums) for the shapes the plain attention
 // kernels do not take: keys and values of different sizes, values that are the first `vd` elements of the cached key
-// rows (a latent that is key and value at once, hundreds of elements long, shared by all query heads), a window, a
-// sink per head.  Prompt portions and decoded tokens alike.
+// rows (a latent that is key and value at once, hundreds of elements long, shared by all query heads), a window, first
+// tokens that stay visible behind the window, chunks, capped scores, a sink per head, a gate per (token, head).  Prompt
+// portions and decoded tokens alike.
 //
 // A block works on 32 query rows - the heads of one key/value head's group for as many consecutive tokens of one
 // request as fit (32 / heads), or 32 of one token's heads - against tiles of 32 keys aligned to absolute positions.
@@ -42,7 +43,10 @@ struct TcParams {
     float* part_o;
     float* part_ml;
     int table_stride, page_size, num_pages, n_tokens, H, G, kd, vd, v_row, v_shared, window, splits, hp, tpt, head_tiles;
-    float scale;
+    int keep_first, chunk;        // positions below keep_first stay visible behind a window; chunk > 0: keys of the query's own run only
+    float scale, softcap;         // softcap > 0: score = softcap * tanh(score / softcap)
+    const bf16* gate;             // [n_tokens, H] with row stride ld_gate, or null: sigmoid(gate) multiplies the head's output
+    long long ld_gate;
     int* status;
 };
 
@@ -111,10 +115,16 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
     if (trow < 0 || n_tok <= 0) return;                                   // a padding row of a captured step
     const int32_t* table = p.block_table + (size_t)trow * p.table_stride;
     const int p0 = p.positions[tok_first], p1 = p.positions[tok_first + n_tok - 1];
-    const int lo_tile = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
+    const int lo_tile = p.window > 0 ? max(0, p0 - p.window + 1) : (p.chunk > 0 ? p0 - p0 % p.chunk : 0);
     const int first_kt = lo_tile / TC_KEYS, last_kt = p1 / TC_KEYS;
-    const int chunk = (last_kt - first_kt + 1 + p.splits - 1) / p.splits;
-    const int kt_begin = first_kt + z * chunk, kt_end = min(last_kt + 1, kt_begin + chunk);
+    // the tiles of the kept first tokens that lie wholly before the first tile of the rows' own range come first; the
+    // walk below counts both runs through (index v -> tile kt_of(v))
+    const int keep_tiles = p.window > 0 ? min((min(p.keep_first, lo_tile) + TC_KEYS - 1) / TC_KEYS, first_kt) : 0;
+    const int n_walk = keep_tiles + last_kt - first_kt + 1;
+    const int per_split = (n_walk + p.splits - 1) / p.splits;
+    const int kt_begin = z * per_split, kt_end = min(n_walk, kt_begin + per_split);
+    auto kt_of = [&](int v) { return v < keep_tiles ? v : first_kt + (v - keep_tiles); };
+    auto in_range = [&](int j) { return j <= p1 && (j >= lo_tile || j < p.keep_first); };
 
     if (tid < TC_ROWS) {
         const int ti = tid / p.hp, hi = tid % p.hp;
@@ -122,8 +132,8 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
         const int t = tok_first + ti;
         row_pos[tid] = valid ? p.positions[t] : -1;
         row_q[tid] = valid ? t * p.H + g * group + ht * p.hp + hi : -1;
-        const int j = kt_begin * TC_KEYS + tid;
-        int page = (kt_begin < kt_end && j <= p1 && j >= lo_tile) ? table[j / p.page_size] : -1;
+        const int j = kt_of(kt_begin) * TC_KEYS + tid;
+        int page = (kt_begin < kt_end && in_range(j)) ? table[j / p.page_size] : -1;
         if (page >= p.num_pages) { page = -1; if (p.status) atomicExch(p.status, 6); }
         key_page[tid] = page;
     }
@@ -150,7 +160,7 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     for (int kt = kt_begin; kt < kt_end; ++kt) {
-        const int kbase = kt * TC_KEYS;
+        const int kbase = kt_of(kt) * TC_KEYS;
         {
             const int page = key_page[ld_row];
             const int in_page = (kbase + ld_row) % p.page_size;
@@ -211,8 +221,10 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
         for (int e = 0; e < 4; ++e) {
             const int pos = e < 2 ? pos0 : pos1;
             const int key = keyc + (e & 1), j = kbase + key;
-            const bool ok = pos >= 0 && j <= pos && (p.window <= 0 || j > pos - p.window) && key_page[key] >= 0;
-            s[e] = ok ? s[e] * p.scale : -INFINITY;
+            const bool ok = pos >= 0 && j <= pos && (p.window <= 0 || j > pos - p.window || j < p.keep_first) &&
+                            (p.chunk <= 0 || j >= pos - pos % p.chunk) && key_page[key] >= 0;
+            const float sc = s[e] * p.scale;
+            s[e] = ok ? (p.softcap > 0.f ? p.softcap * tanhf(sc / p.softcap) : sc) : -INFINITY;
         }
         const float mx0 = quad_max(fmaxf(s[0], s[1])), mx1 = quad_max(fmaxf(s[2], s[3]));
         if ((lane & 3) == 0) { m_part[row0 * 4 + c] = mx0; m_part[row1 * 4 + c] = mx1; }
@@ -251,8 +263,8 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
             }
         }
         if (tid < TC_KEYS) {                                              // the next tile's pages
-            const int j = (kt + 1) * TC_KEYS + tid;
-            int page = (kt + 1 < kt_end && j <= p1 && j >= lo_tile) ? table[j / p.page_size] : -1;
+            const int j = kt_of(kt + 1) * TC_KEYS + tid;
+            int page = (kt + 1 < kt_end && in_range(j)) ? table[j / p.page_size] : -1;
             if (page >= p.num_pages) { page = -1; if (p.status) atomicExch(p.status, 6); }
             // written after everybody has read this tile's entries: they were last read before barrier (3)
             key_page[tid] = page;
@@ -282,7 +294,11 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
         if (q0 >= 0) { const float sk = p.sink[q0 % p.H], mf = fmaxf(m0, sk); f0 = m0 == -INFINITY ? 0.f : expf(m0 - mf); l0 = l0 * f0 + expf(sk - mf); }
         if (q1 >= 0) { const float sk = p.sink[q1 % p.H], mf = fmaxf(m1, sk); f1 = m1 == -INFINITY ? 0.f : expf(m1 - mf); l1 = l1 * f1 + expf(sk - mf); }
     }
-    const float inv0 = l0 > 0.f ? f0 / l0 : 0.f, inv1 = l1 > 0.f ? f1 / l1 : 0.f;
+    float inv0 = l0 > 0.f ? f0 / l0 : 0.f, inv1 = l1 > 0.f ? f1 / l1 : 0.f;
+    if (p.gate != nullptr) {
+        if (q0 >= 0) inv0 *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)(q0 / p.H) * p.ld_gate + q0 % p.H])));
+        if (q1 >= 0) inv1 *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)(q1 / p.H) * p.ld_gate + q1 % p.H])));
+    }
     if (q0 >= 0) {
         bf16* dst = p.out + (size_t)q0 * vd + col0 + (lane & 3) * 2;
 #pragma unroll
@@ -301,6 +317,7 @@ __global__ void __launch_bounds__(256, 2) attention_paged_tc_kernel(TcParams p) 
 #define TC_MAX_SPLITS 64
 __global__ void __launch_bounds__(128) attention_paged_tc_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                        const float* __restrict__ sink, const int32_t* __restrict__ table_row,
+                                                                       const bf16* __restrict__ gate, long long ld_gate,
                                                                        bf16* __restrict__ out, int H, int vd, int splits) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
@@ -316,7 +333,8 @@ __global__ void __launch_bounds__(128) attention_paged_tc_merge_kernel(const flo
         const float M = fmaxf(pb_warp_max(fmaxf(ma, mb)), sk);
         const float wa = ma == -INFINITY ? 0.f : expf(ma - M), wb = mb == -INFINITY ? 0.f : expf(mb - M);
         const float L = pb_warp_sum(la * wa + lb * wb) + (sink ? expf(sk - M) : 0.f);
-        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        float inv = L > 0.f ? 1.0f / L : 0.f;
+        if (gate != nullptr) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(row / H) * ld_gate + row % H])));
         w_s[lane] = wa * inv;
         w_s[lane + 32] = wb * inv;
     }
@@ -364,15 +382,19 @@ PB_API long long pb_attention_paged_tc_scratch_floats(int n_tokens, int H, int v
 // q [n_tokens, H, kd], out [n_tokens, H, vd], pages [num_pages, G, page_size, kd] (values: [.., v_row], or the key pages
 // themselves with v_shared); tiles: tile_seq/tile_tok0 [n_tiles] (request of the batch, first token within its portion) with
 // cu_q, or null: tile i is token i alone (a step of single tokens).  scratch: float32 of pb_attention_paged_tc_scratch_floats.
+// window, keep_first, chunk, softcap, gate: as for pb_attention_paged.
 PB_API int pb_attention_paged_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const float* sink,
                                       const int32_t* positions, const int32_t* table_row, const int32_t* block_table, int table_stride,
                                       const int32_t* cu_q, const int32_t* tile_seq, const int32_t* tile_tok0, int n_tiles, int page_size,
                                       int num_pages, int n_tokens, int H, int G, int kd, int vd, int v_row, int v_shared, float scale,
-                                      int window, int splits, float* scratch, int* status, cudaStream_t stream) {
+                                      int window, int keep_first, int chunk, float softcap, const void* gate, long long ld_gate,
+                                      int splits, float* scratch, int* status, cudaStream_t stream) {
     PB_REQUIRE(pb_attention_paged_tc_supported(H, G, kd, vd, v_shared), "attention_paged_tc: shape H=%d G=%d kd=%d vd=%d not taken", H, G, kd, vd);
     PB_REQUIRE(q && k_pages && v_pages && out && positions && table_row && block_table, "attention_paged_tc: null pointer");
     PB_REQUIRE(page_size > 0 && num_pages > 0 && table_stride > 0 && n_tiles >= 0 && n_tokens >= 0, "attention_paged_tc: bad geometry");
     PB_REQUIRE(tile_seq == nullptr || (tile_tok0 && cu_q), "attention_paged_tc: a list of tiles needs the portions' offsets");
+    PB_REQUIRE(keep_first >= 0 && chunk >= 0 && !(window > 0 && chunk > 0) && (gate == nullptr || ld_gate >= H),
+               "attention_paged_tc: window %d, kept %d, chunk %d", window, keep_first, chunk);
     PB_REQUIRE(splits >= 1 && splits <= TC_MAX_SPLITS && (splits == 1 || (scratch && pb_aligned(scratch, 16))), "attention_paged_tc: %d splits", splits);
     PB_REQUIRE(pb_aligned(q, 16) && pb_aligned(k_pages, 16) && pb_aligned(v_pages, 16) && pb_aligned(out, 4) && (v_shared || v_row % 8 == 0),
                "attention_paged_tc: operands must be 16-byte aligned");
@@ -389,6 +411,7 @@ PB_API int pb_attention_paged_tc_bf16(const void* q, const void* k_pages, const 
     p.tpt = tile_seq ? TC_ROWS / p.hp : 1;
     p.head_tiles = (group + p.hp - 1) / p.hp;
     p.scale = scale; p.status = status;
+    p.keep_first = window > 0 ? keep_first : 0; p.chunk = chunk; p.softcap = softcap; p.gate = (const bf16*)gate; p.ld_gate = ld_gate;
     const size_t smem = tc_smem(kd, vd, v_shared);
     const dim3 grid(n_tiles, G * p.head_tiles, splits);
     PB_REQUIRE(G * p.head_tiles < 65536, "attention_paged_tc: too many head tiles");
@@ -410,7 +433,7 @@ PB_API int pb_attention_paged_tc_bf16(const void* q, const void* k_pages, const 
     PB_CHECK_LAUNCH("attention_paged_tc");
     if (splits > 1) {
         pb_launch(attention_paged_tc_merge_kernel, dim3(n_tokens * H), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, sink,
-                  table_row, (bf16*)out, H, vd, splits);
+                  table_row, (const bf16*)gate, ld_gate, (bf16*)out, H, vd, splits);
         PB_CHECK_LAUNCH("attention_paged_tc_merge");
     }
     return 0;

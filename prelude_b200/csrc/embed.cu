@@ -97,3 +97,29 @@ PB_API int pb_embed_sinusoid(const int32_t* ids, const int32_t* positions, const
     PB_CHECK_LAUNCH("embed_sinusoid");
     return 0;
 }
+
+
+// The same with every row multiplied by a constant: res[t, :] = table[ids[t], :] * scale (the product in float32).
+template <typename T>
+__global__ void embed_gather_scaled_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table, float scale,
+                                           float* __restrict__ out, int n_tokens, int width, int vocab) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* dst = out + (size_t)t * width;
+    const bool ok = id >= 0 && id < vocab;      // the host validates ids; never read out of bounds
+    const T* src = table + (size_t)(ok ? id : 0) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = ok ? pb_ld(src + i) * scale : 0.f;
+}
+
+PB_API int pb_embed_gather_scaled(const int32_t* ids, const void* table, int table_dtype, float scale, float* out, int n_tokens,
+                                  int width, int vocab, cudaStream_t stream) {
+    PB_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_gather_scaled: bad sizes T=%d H=%d V=%d", n_tokens, width, vocab);
+    if (n_tokens == 0) return 0;
+    PB_DISPATCH_DTYPE(table_dtype, T,
+        (pb_launch(embed_gather_scaled_kernel<T>, dim3(n_tokens), dim3(width >= 1024 ? 256 : 128), 0, stream, ids, (const T*)table, scale, out,
+                   n_tokens, width, vocab)));
+    PB_CHECK_LAUNCH("embed_gather_scaled");
+    return 0;
+}

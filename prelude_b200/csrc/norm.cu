@@ -476,3 +476,124 @@ PB_API int pb_normed_add_rmsnorm(const void* x, const float* wx, float eps_x, fl
     PB_CHECK_LAUNCH("normed_add_rmsnorm");
     return 0;
 }
+
+
+// A sublayer's output that joins the residual stream times a constant: res += scale * x ; y = rmsnorm(res) * w, one
+// block per row, float32.  With `rows` only the chosen rows are made and res is left alone (the final norm at the
+// places whose logits are wanted).  x as for pb_add_rmsnorm: of type dtype, or x_parts float32 arrays whose sum,
+// taken in ascending order, is what is scaled and added.
+template <typename TX, typename TY>
+__global__ void scaled_add_rmsnorm_kernel(const TX* __restrict__ x, int n_parts, size_t part_stride, float scale, float* __restrict__ res,
+                                          const int32_t* __restrict__ rows, int n_rows_total, const float* __restrict__ w,
+                                          TY* __restrict__ y, int width, float eps) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    __shared__ float red[32];
+    const int src = rows ? rows[blockIdx.x] : (int)blockIdx.x;
+    TY* out = y + (size_t)blockIdx.x * width;
+    if (src < 0 || src >= n_rows_total) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(out + i, 0.f);
+        return;
+    }
+    float* r = res + (size_t)src * width;
+    const TX* xr = x + (size_t)src * width;
+    auto value = [&](int i) {
+        float a = pb_ld(xr + i);
+        for (int s = 1; s < n_parts; ++s) a += pb_ld(xr + s * part_stride + i);
+        return fmaf(scale, a, r[i]);
+    };
+    constexpr int KEEP = 16;
+    float kept[KEEP];
+    const bool fits = width <= KEEP * (int)blockDim.x;
+    float ss = 0.f;
+    if (fits) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            kept[k] = i < width ? value(i) : 0.f;
+            ss += kept[k] * kept[k];
+        }
+        if (rows == nullptr) {
+#pragma unroll
+            for (int k = 0; k < KEEP; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                if (i < width) r[i] = kept[k];
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = value(i);
+            if (rows == nullptr) r[i] = v;
+            ss += v * v;
+        }
+    }
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps);
+    if (fits) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < width) pb_st(out + i, kept[k] * inv * w[i]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) pb_st(out + i, (rows ? value(i) : r[i]) * inv * w[i]);
+    }
+}
+
+PB_API int pb_scaled_add_rmsnorm(const void* x, int x_parts, long long part_stride, float scale, float* res, const int32_t* rows,
+                                 int n_out, int n_rows_total, const float* w, void* y, int dtype, int width, float eps,
+                                 cudaStream_t stream) {
+    PB_REQUIRE(n_out >= 0 && width > 0 && n_rows_total >= 0, "scaled_add_rmsnorm: bad sizes");
+    PB_REQUIRE(x && res && w && y, "scaled_add_rmsnorm: null pointer");
+    PB_REQUIRE(x_parts >= 0 && x_parts <= 64 && (x_parts == 0 || part_stride >= (long long)n_rows_total * width),
+               "scaled_add_rmsnorm: %d parts %lld apart", x_parts, part_stride);
+    PB_REQUIRE(rows != nullptr || n_out == n_rows_total, "scaled_add_rmsnorm: without chosen rows every row is made");
+    if (n_out == 0) return 0;
+    if (x_parts > 0) {
+        PB_DISPATCH_DTYPE(dtype, T,
+            (pb_launch(scaled_add_rmsnorm_kernel<float, T>, dim3(n_out), dim3(norm_threads(width)), 0, stream, (const float*)x, x_parts,
+                       (size_t)part_stride, scale, res, rows, n_rows_total, w, (T*)y, width, eps)));
+    } else {
+        PB_DISPATCH_DTYPE(dtype, T,
+            (pb_launch(scaled_add_rmsnorm_kernel<T, T>, dim3(n_out), dim3(norm_threads(width)), 0, stream, (const T*)x, 1, (size_t)0, scale,
+                       res, rows, n_rows_total, w, (T*)y, width, eps)));
+    }
+    PB_CHECK_LAUNCH("scaled_add_rmsnorm");
+    return 0;
+}
+
+// Two outputs side by side, each brought to unit root mean square over the row and scaled, then added:
+// out = sa * a / rms(a) * wa + sb * b / rms(b) * wb, computed and handed out in float32 (what the residual add takes as
+// a sum of one part).  One block per row.
+template <typename T>
+__global__ void normed_pair_sum_kernel(const T* __restrict__ a, const float* __restrict__ wa, float sa, const T* __restrict__ b,
+                                       const float* __restrict__ wb, float sb, float eps, float* __restrict__ out, int width) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const T* ar = a + row * width;
+    const T* br = b + row * width;
+    float ssa = 0.f, ssb = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float va = pb_ld(ar + i), vb = pb_ld(br + i);
+        ssa += va * va;
+        ssb += vb * vb;
+    }
+    const float ta = block_sum(ssa, red), tb = block_sum(ssb, red);
+    const float ia = sa / sqrtf(ta / (float)width + eps), ib = sb / sqrtf(tb / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        out[row * width + i] = pb_ld(ar + i) * ia * wa[i] + pb_ld(br + i) * ib * wb[i];
+}
+
+PB_API int pb_normed_pair_sum(const void* a, const float* wa, float sa, const void* b, const float* wb, float sb, float eps, float* out,
+                              int dtype, int rows, int width, cudaStream_t stream) {
+    PB_REQUIRE(rows >= 0 && width > 0, "normed_pair_sum: bad sizes");
+    PB_REQUIRE(a && wa && b && wb && out, "normed_pair_sum: null pointer");
+    if (rows == 0) return 0;
+    PB_DISPATCH_DTYPE(dtype, T,
+        (pb_launch(normed_pair_sum_kernel<T>, dim3(rows), dim3(norm_threads(width)), 0, stream, (const T*)a, wa, sa, (const T*)b, wb, sb, eps,
+                   out, width)));
+    PB_CHECK_LAUNCH("normed_pair_sum");
+    return 0;
+}

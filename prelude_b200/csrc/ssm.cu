@@ -6,7 +6,8 @@
 //   pb_ssm_scan             dt = softplus(dt + bias); S <- exp(-exp(A_log) dt) S + dt B x^T; y = S^T C + D x, token by
 //                           token, the state [heads, state, head_dim] float32 per sequence, read at the start and written
 //                           at the end of the step
-//   pb_gated_group_rmsnorm  y * silu(z), brought to unit root mean square in equal parts, times a scale
+//   pb_gated_group_rmsnorm  y * silu(z), brought to unit root mean square in equal parts, times a scale; or, with the gate
+//                           after the norm, y brought to unit root mean square in equal parts, times a scale, times silu(z)
 //
 // Decay, step size, softplus, exponentials, the state and the sums over it are float32 whatever the run's type;
 // the projections and the convolution's output are of the run's type.  A sequence's tokens are visited in order,
@@ -59,7 +60,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, long long ld_i
     if (seq < 0) return;                                   // a padding row
     const int i = positions[t] - q_start[seq];             // the token's index among its sequence's tokens of this step
     const T* old = carried + (size_t)slots[seq] * (taps - 1) * channels;
-    float acc = bias[c];
+    float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
         const int idx = i - (taps - 1 - j);                // in-step index of the input under tap j
         const float x = idx >= 0 ? pb_ld(in + (size_t)(t - (taps - 1 - j)) * ld_in + c)
@@ -86,7 +87,7 @@ __global__ void causal_conv_silu_vec_kernel(const T* __restrict__ in, long long 
     float wt[VN][TAPS], bs[VN];
 #pragma unroll
     for (int e = 0; e < VN; ++e) {
-        bs[e] = bias[c + e];
+        bs[e] = bias ? bias[c + e] : 0.f;
 #pragma unroll
         for (int j = 0; j < TAPS; ++j) wt[e][j] = w[(size_t)(c + e) * TAPS + j];
     }
@@ -313,7 +314,8 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
 // ---------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long ld_z,
-                                           const float* __restrict__ w, T* __restrict__ out, int inner, int parts, float eps) {
+                                           const float* __restrict__ w, T* __restrict__ out, int inner, int parts, float eps,
+                                           int gate_after) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     __shared__ float red[32];
@@ -321,7 +323,7 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     const float* yr = y + (size_t)t * inner + (size_t)part * width;
     const T* zr = z + (size_t)t * ld_z + (size_t)part * width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = yr[i] * silu_f(pb_ld(zr + i)); ss += v * v; }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = gate_after ? yr[i] : yr[i] * silu_f(pb_ld(zr + i)); ss += v * v; }
     ss = pb_warp_sum(ss);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     if (lane == 0) red[warp] = ss;
@@ -331,7 +333,7 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     const float inv = 1.0f / sqrtf(total / (float)width + eps);
     T* o = out + (size_t)t * inner + (size_t)part * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x)
-        pb_st(o + i, yr[i] * silu_f(pb_ld(zr + i)) * inv * w[(size_t)part * width + i]);
+        pb_st(o + i, yr[i] * silu_f(pb_ld(zr + i)) * inv * w[(size_t)part * width + i]);   // the same product either way
 }
 
 template <typename TI, typename TO>
@@ -350,7 +352,7 @@ PB_API int pb_causal_conv_silu(const void* in, long long ld_in, const float* w, 
                                int dtype, const int32_t* token_seq, const int32_t* positions, const int32_t* q_start,
                                const int32_t* slots, int n_tokens, int channels, int taps, cudaStream_t stream) {
     PB_REQUIRE(n_tokens >= 0 && channels > 0 && taps >= 1 && ld_in >= channels, "causal_conv_silu: bad sizes");
-    PB_REQUIRE(in && w && bias && out && token_seq && positions && q_start && slots && (taps == 1 || carried), "causal_conv_silu: null pointer");
+    PB_REQUIRE(in && w && out && token_seq && positions && q_start && slots && (taps == 1 || carried), "causal_conv_silu: null pointer");
     if (n_tokens == 0) return 0;
     PB_REQUIRE((channels + 127) / 128 < 65536, "causal_conv_silu: %d channels in one launch", channels);
     const int vn = dtype == PB_BF16 ? 8 : 4;
@@ -413,9 +415,9 @@ PB_API int pb_ssm_scan(const void* u, const void* dt_in, long long ld_dt, int dt
 }
 
 // y float32 [n_tokens, inner]; z: the gate columns of the input projection, row stride ld_z; w float32 [inner];
-// out [n_tokens, inner] dense.
+// out [n_tokens, inner] dense.  gate_after 0: norm(y * silu(z)) * w; 1: norm(y) * w * silu(z).
 PB_API int pb_gated_group_rmsnorm(const float* y, const void* z, long long ld_z, const float* w, void* out, int dtype, int n_tokens,
-                                  int inner, int parts, float eps, cudaStream_t stream) {
+                                  int inner, int parts, float eps, int gate_after, cudaStream_t stream) {
     PB_REQUIRE(n_tokens >= 0 && inner > 0 && parts > 0 && inner % parts == 0 && ld_z >= inner, "gated_group_rmsnorm: bad sizes");
     PB_REQUIRE(y && z && w && out, "gated_group_rmsnorm: null pointer");
     if (n_tokens == 0) return 0;
@@ -424,7 +426,7 @@ PB_API int pb_gated_group_rmsnorm(const float* y, const void* z, long long ld_z,
     while (threads < 256 && threads < inner / parts) threads <<= 1;
     PB_DISPATCH_DTYPE(dtype, T,
         (pb_launch(gated_group_rmsnorm_kernel<T>, dim3(n_tokens, parts), dim3(threads), 0, stream, y, (const T*)z, ld_z, w, (T*)out, inner,
-                   parts, eps)));
+                   parts, eps, gate_after)));
     PB_CHECK_LAUNCH("gated_group_rmsnorm");
     return 0;
 }

@@ -684,9 +684,13 @@ def qkv_prepare(q_in: torch.Tensor, k_in: Optional[torch.Tensor], v_in: Optional
 def attention_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[torch.Tensor], value_dim: int, positions: torch.Tensor,
                     table_row: torch.Tensor, block_table: torch.Tensor, scale: float, window: Optional[int] = None,
                     sink: Optional[torch.Tensor] = None, swizzle_k: bool = False, swizzle_v: bool = False,
-                    status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, keep_first: int = 0,
+                    chunk: Optional[int] = None, softcap: Optional[float] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [T, H, kd] against pages [P, G, page, kd]; values from ``v_pages`` [P, Gv, page, value_dim], or, with
-    ``v_pages`` None, the first ``value_dim`` elements of the key rows.  float32 arithmetic; see csrc/attention_paged.cu."""
+    ``v_pages`` None, the first ``value_dim`` elements of the key rows.  ``keep_first``: positions below it stay visible
+    behind the window; ``chunk``: keys of the query's own run of positions only; ``softcap``: scores capped by tanh;
+    ``gate`` [T, H] (a view with dense rows): its sigmoid multiplies the head's output.  float32 arithmetic; see
+    csrc/attention_paged.cu."""
     _need(q, "q")
     _need(k_pages, "k_pages", q.dtype)
     _need(positions, "positions", torch.int32)
@@ -710,6 +714,10 @@ def attention_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[to
         _need(sink, "sink", torch.float32)
         if sink.numel() != H:
             raise KernelLibraryError("attention_paged: one sink per query head")
+    if gate is not None:
+        _need(gate, "gate", q.dtype, contiguous=False)
+        if tuple(gate.shape) != (T, H) or gate.stride(1) != 1:
+            raise KernelLibraryError("attention_paged: one gate per token and query head, rows dense")
     if out is None:
         out = torch.empty((T, H, value_dim), dtype=q.dtype, device=q.device)
     else:
@@ -719,26 +727,28 @@ def attention_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[to
     check(_l.library().pb_attention_paged(
         q.data_ptr(), k_pages.data_ptr(), vp.data_ptr(), out.data_ptr(), dtype_code(q.dtype), _ptr(sink), positions.data_ptr(),
         table_row.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, num_pages, T, H, G, kd, value_dim, v_row, Gv,
-        float(scale), int(window or 0), 1 if swizzle_k else 0, 1 if swizzle_v else 0, _ptr(status), _stream()), "attention_paged")
+        float(scale), int(window or 0), int(keep_first or 0), int(chunk or 0), float(softcap or 0.0), _ptr(gate),
+        0 if gate is None else gate.stride(0), 1 if swizzle_k else 0, 1 if swizzle_v else 0, _ptr(status), _stream()), "attention_paged")
     return out
 
 
 # -- the state-space mixer ------------------------------------------------------------------------------------------
-def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, carried: torch.Tensor, batch,
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], carried: torch.Tensor, batch,
                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """silu(conv(x) + bias) per channel; x [T, C] a view with dense rows, weight float32 [C, taps], carried
-    [slots, taps - 1, C] of x's type (the sequences' last inputs of earlier steps)."""
+    """silu(conv(x) + bias) per channel; x [T, C] a view with dense rows, weight float32 [C, taps], bias float32 [C] or
+    None, carried [slots, taps - 1, C] of x's type (the sequences' last inputs of earlier steps)."""
     _need(x, "x", contiguous=False)
     _need(weight, "weight", torch.float32)
-    _need(bias, "bias", torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
     _need(carried, "carried", x.dtype)
     T, C = x.shape
     taps = weight.shape[1]
-    if x.stride(1) != 1 or weight.shape[0] != C or bias.numel() != C or tuple(carried.shape[1:]) != (taps - 1, C):
+    if x.stride(1) != 1 or weight.shape[0] != C or (bias is not None and bias.numel() != C) or tuple(carried.shape[1:]) != (taps - 1, C):
         raise KernelLibraryError(f"causal_conv_silu: x {tuple(x.shape)}, weight {tuple(weight.shape)}, carried {tuple(carried.shape)}")
     if out is None:
         out = torch.empty((T, C), dtype=x.dtype, device=x.device)
-    check(_l.library().pb_causal_conv_silu(x.data_ptr(), x.stride(0), weight.data_ptr(), bias.data_ptr(), carried.data_ptr(),
+    check(_l.library().pb_causal_conv_silu(x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), carried.data_ptr(),
                                            out.data_ptr(), dtype_code(x.dtype), batch.token_seq.data_ptr(), batch.positions.data_ptr(),
                                            batch.q_start.data_ptr(), batch.state_slots.data_ptr(), T, C, taps, _stream()),
           "causal_conv_silu")
@@ -775,8 +785,9 @@ def ssm_scan(u: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: to
 
 
 def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int, eps: float,
-                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y * silu(z) brought to unit root mean square in ``parts`` equal parts, times weight; y float32 [T, inner], z a view
+                        out: Optional[torch.Tensor] = None, gate_after: bool = False) -> torch.Tensor:
+    """y * silu(z) brought to unit root mean square in ``parts`` equal parts, times weight; with ``gate_after`` y
+    brought to unit root mean square in parts, times weight, times silu(z).  y float32 [T, inner], z a view
     [T, inner] with dense rows of the run's type, which the result has too."""
     _need(y, "y", torch.float32)
     _need(z, "z", contiguous=False)
@@ -787,7 +798,8 @@ def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, 
     if out is None:
         out = torch.empty((T, inner), dtype=z.dtype, device=y.device)
     check(_l.library().pb_gated_group_rmsnorm(y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(),
-                                              dtype_code(z.dtype), T, inner, parts, float(eps), _stream()), "gated_group_rmsnorm")
+                                              dtype_code(z.dtype), T, inner, parts, float(eps), 1 if gate_after else 0, _stream()),
+          "gated_group_rmsnorm")
     return out
 
 
@@ -800,4 +812,199 @@ def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float, out_dtype
     out = torch.empty(a.shape, dtype=out_dtype, device=a.device)
     check(_l.library().pb_scaled_sum(a.data_ptr(), float(sa), b.data_ptr(), float(sb), out.data_ptr(), dtype_code(a.dtype),
                                      dtype_code(out_dtype), a.numel(), _stream()), "scaled_sum")
+    return out
+
+
+# -- a residual stream that takes its sublayers' outputs times a constant ------------------------------------------------
+class Scaled:
+    """A sublayer's output that joins the residual stream times a constant: the value is ``scale * x`` (x a tensor of
+    the run's type or ``PartialSums``), not computed yet.  The fused residual add multiplies while it adds, in float32."""
+
+    def __init__(self, x, scale: float):
+        self.x, self.scale = x, float(scale)
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+
+def scaled_add_rmsnorm(x: "Scaled", res: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                       rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """res += scale * x (in place, unless ``rows`` picks rows: then res is left alone); returns rmsnorm(res) * weight in
+    ``out_dtype`` for every row, or for the chosen ones."""
+    _need(res, "res", torch.float32)
+    _need(weight, "weight", torch.float32)
+    total, width = res.shape
+    if tuple(x.shape) != tuple(res.shape) or weight.numel() != width:
+        raise KernelLibraryError(f"scaled_add_rmsnorm: x {tuple(x.shape)} against residual {tuple(res.shape)}")
+    ptr, parts, stride = _x_args(x.x, out_dtype, "x")
+    n_out = total
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n_out = rows.numel()
+    out = torch.empty((n_out, width), dtype=out_dtype, device=res.device)
+    check(_l.library().pb_scaled_add_rmsnorm(ptr, parts, stride, x.scale, res.data_ptr(), _ptr(rows), n_out, total, weight.data_ptr(),
+                                             out.data_ptr(), dtype_code(out_dtype), width, float(eps), _stream()), "scaled_add_rmsnorm")
+    return out
+
+
+def normed_pair_sum(a: torch.Tensor, wa: torch.Tensor, sa: float, b: torch.Tensor, wb: torch.Tensor, sb: float, eps: float) -> PartialSums:
+    """sa * a / rms(a) * wa + sb * b / rms(b) * wb over the rows of a and b [T, width], in float32: returned as a sum of
+    one part, which the residual add takes without a rounding in between."""
+    _need(a, "a")
+    _need(b, "b", a.dtype)
+    _need(wa, "wa", torch.float32)
+    _need(wb, "wb", torch.float32)
+    T, width = a.shape
+    if a.shape != b.shape or wa.numel() != width or wb.numel() != width:
+        raise KernelLibraryError(f"normed_pair_sum: {tuple(a.shape)} against {tuple(b.shape)}")
+    out = torch.empty((1, T, width), dtype=torch.float32, device=a.device)
+    check(_l.library().pb_normed_pair_sum(a.data_ptr(), wa.data_ptr(), float(sa), b.data_ptr(), wb.data_ptr(), float(sb), float(eps),
+                                          out.data_ptr(), dtype_code(a.dtype), T, width, _stream()), "normed_pair_sum")
+    return PartialSums(out)
+
+
+def embed_gather_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+    """res[t, :] = table[ids[t], :] * scale as float32 (the residual stream)."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    T, (V, H) = ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    check(_l.library().pb_embed_gather_scaled(ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), float(scale), out.data_ptr(),
+                                              T, H, V, _stream()), "embed_gather_scaled")
+    return out
+
+
+def tanh_(x: torch.Tensor) -> torch.Tensor:
+    """tanh of a dense tensor, in place (float32 arithmetic)."""
+    _need(x, "x")
+    check(_l.library().pb_tanh(x.data_ptr(), x.data_ptr(), dtype_code(x.dtype), x.numel(), _stream()), "tanh")
+    return x
+
+
+def _rows_view(t: torch.Tensor, name: str, rows: int, dtype) -> None:
+    _need(t, name, dtype, contiguous=False)
+    if t.dim() != 2 or t.stride(1) != 1 or t.shape[0] != rows:
+        raise KernelLibraryError(f"{name} must be [tokens, cols] with dense rows, is {tuple(t.shape)}")
+
+
+def heads_prepare(q_in: torch.Tensor, k_in: Optional[torch.Tensor], v_in: Optional[torch.Tensor], *, n_heads: int, q_dim: int,
+                  q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                  rates: Optional[torch.Tensor] = None, rot_dims: int = 0, adjacent: bool = False,
+                  v_other: Optional[torch.Tensor] = None, v_copy: Optional[torch.Tensor] = None, mix: float = 0.0,
+                  positions: torch.Tensor, table_row: torch.Tensor, block_table: Optional[torch.Tensor] = None,
+                  q_out: torch.Tensor, k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                  status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-head norm (one scale for all heads), rotation by rates, values blended with another layer's; queries to
+    ``q_out``, keys and values into pages; see csrc/heads_prepare.cu.  ``q_in``, ``k_in``, ``v_in`` are [T, cols] views
+    with dense rows; ``v_other`` / ``v_copy`` dense [T, value cols]; ``k_pages`` None: nothing is cached."""
+    T, dt = q_in.shape[0], q_in.dtype
+    _rows_view(q_in, "q_in", T, dt)
+    for t, name in ((q_weight, "q_weight"), (k_weight, "k_weight"), (rates, "rates")):
+        if t is not None:
+            _need(t, name, torch.float32)
+    _need(positions, "positions", torch.int32)
+    _need(table_row, "table_row", torch.int32)
+    _need(q_out, "q_out", dt)
+    if q_in.shape[1] != n_heads * q_dim or q_out.numel() != T * n_heads * q_dim:
+        raise KernelLibraryError(f"heads_prepare: q_in {tuple(q_in.shape)}, q_out {tuple(q_out.shape)} for {n_heads} heads of {q_dim}")
+    if q_weight is not None and q_weight.numel() != q_dim:
+        raise KernelLibraryError("heads_prepare: the query norm's scale covers one head")
+    if rates is not None and rates.numel() * 2 != rot_dims:
+        raise KernelLibraryError("heads_prepare: one rate per rotated pair")
+    G = kd = Gv = vd = page_size = num_pages = stride = ld_other = 0
+    if k_pages is not None:
+        _need(k_pages, "k_pages", dt)
+        _need(block_table, "block_table", torch.int32)
+        num_pages, G, page_size, kd = k_pages.shape
+        stride = block_table.shape[1]
+        if k_in is None:
+            raise KernelLibraryError("heads_prepare: key pages without keys")
+        _rows_view(k_in, "k_in", T, dt)
+        if k_in.shape[1] != G * kd or (k_weight is not None and k_weight.numel() != kd):
+            raise KernelLibraryError(f"heads_prepare: keys {tuple(k_in.shape)} against pages {tuple(k_pages.shape)}")
+        if v_pages is not None:
+            _need(v_pages, "v_pages", dt)
+            _, Gv, _, vd = v_pages.shape
+            if v_in is None:
+                raise KernelLibraryError("heads_prepare: value pages without values")
+            _rows_view(v_in, "v_in", T, dt)
+            if v_in.shape[1] != Gv * vd or v_pages.shape[0] != num_pages or v_pages.shape[2] != page_size:
+                raise KernelLibraryError(f"heads_prepare: values {tuple(v_in.shape)} against pages {tuple(v_pages.shape)}")
+            for t, name in ((v_other, "v_other"), (v_copy, "v_copy")):
+                if t is not None:
+                    _need(t, name, dt)
+                    if tuple(t.shape) != (T, Gv * vd):
+                        raise KernelLibraryError(f"heads_prepare: {name} {tuple(t.shape)} against values {tuple(v_in.shape)}")
+                    ld_other = Gv * vd
+    elif v_other is not None or v_copy is not None:
+        raise KernelLibraryError("heads_prepare: blended values need pages")
+    check(_l.library().pb_heads_prepare(
+        q_in.data_ptr(), q_in.stride(0), _ptr(k_in), 0 if k_in is None else k_in.stride(0), _ptr(v_in),
+        0 if v_in is None else v_in.stride(0), dtype_code(dt), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(rates), int(rot_dims),
+        1 if adjacent else 0, _ptr(v_other), _ptr(v_copy), ld_other, float(mix), positions.data_ptr(), table_row.data_ptr(),
+        _ptr(block_table), stride, page_size, num_pages, q_out.data_ptr(), _ptr(k_pages), _ptr(v_pages), T, n_heads, q_dim, G, kd, Gv,
+        vd, _ptr(status), _stream()), "heads_prepare")
+    return q_out
+
+
+def gated_delta_scan(u: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                     state: torch.Tensor, batch, kv_heads: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The gated delta rule over the step's tokens, sequence by sequence; u [T, 2 G D + H E] laid out [q | k | v] (the
+    convolutions' outputs), beta and a [T, H] views with dense rows, state float32 [slots, H, D, E]; returns o float32
+    [T, H E].  See csrc/delta_rule.cu."""
+    T = u.shape[0]
+    _rows_view(u, "u", T, None)
+    _rows_view(beta, "beta", T, u.dtype)
+    _rows_view(a, "a", T, u.dtype)
+    for t, name in ((a_log, "a_log"), (dt_bias, "dt_bias"), (state, "state")):
+        _need(t, name, torch.float32)
+    _, H, D, E = state.shape
+    if u.shape[1] != 2 * kv_heads * D + H * E or beta.shape[1] != H or a.shape[1] != H or a_log.numel() != H or dt_bias.numel() != H:
+        raise KernelLibraryError(f"gated_delta_scan: u {tuple(u.shape)}, state {tuple(state.shape)}, {kv_heads} query/key heads")
+    if out is None:
+        out = torch.empty((T, H * E), dtype=torch.float32, device=u.device)
+    check(_l.library().pb_gated_delta_scan(u.data_ptr(), u.stride(0), beta.data_ptr(), beta.stride(0), a.data_ptr(), a.stride(0),
+                                           dtype_code(u.dtype), a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), out.data_ptr(),
+                                           batch.cu_q.data_ptr(), batch.state_slots.data_ptr(), batch.cu_q.numel() - 1, H, kv_heads, D, E,
+                                           _stream()), "gated_delta_scan")
+    return out
+
+
+def token_shift_mix(x: torch.Tensor, carried: torch.Tensor, mu: torch.Tensor, batch, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[s, t] = x_t + (x_(t-1) - x_t) * mu[s]; x [T, width] dense, carried [slots, width] (the sequences' last input of
+    earlier steps), mu float32 [n, width]; returns [n, T, width] of x's type."""
+    _need(x, "x")
+    _need(carried, "carried", x.dtype)
+    _need(mu, "mu", torch.float32)
+    T, width = x.shape
+    n = mu.shape[0]
+    if mu.shape[1] != width or carried.shape[1] != width:
+        raise KernelLibraryError(f"token_shift_mix: x {tuple(x.shape)}, mu {tuple(mu.shape)}, carried {tuple(carried.shape)}")
+    if out is None:
+        out = torch.empty((n, T, width), dtype=x.dtype, device=x.device)
+    check(_l.library().pb_token_shift_mix(x.data_ptr(), carried.data_ptr(), mu.data_ptr(), out.data_ptr(), dtype_code(x.dtype),
+                                          batch.token_seq.data_ptr(), batch.positions.data_ptr(), batch.q_start.data_ptr(),
+                                          batch.state_slots.data_ptr(), T, width, n, _stream()), "token_shift_mix")
+    return out
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, w0: torch.Tensor, bonus: torch.Tensor,
+             state: torch.Tensor, batch, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The decaying-state recurrence with a bonus for the current token over the step's tokens, sequence by sequence; r, k,
+    v, w [T, H D] views with dense rows (w before its exponentials), w0 and bonus float32 [H D], state float32
+    [slots, H, D, D]; returns o float32 [T, H D].  See csrc/wkv.cu."""
+    T = r.shape[0]
+    for t, name in ((r, "r"), (k, "k"), (v, "v"), (w, "w")):
+        _rows_view(t, name, T, r.dtype)
+    for t, name in ((w0, "w0"), (bonus, "bonus"), (state, "state")):
+        _need(t, name, torch.float32)
+    _, H, D, D2 = state.shape
+    if D != D2 or any(t.shape[1] != H * D for t in (r, k, v, w)) or w0.numel() != H * D or bonus.numel() != H * D:
+        raise KernelLibraryError(f"wkv_scan: r {tuple(r.shape)}, state {tuple(state.shape)}")
+    if out is None:
+        out = torch.empty((T, H * D), dtype=torch.float32, device=r.device)
+    check(_l.library().pb_wkv_scan(r.data_ptr(), r.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), w.data_ptr(),
+                                   w.stride(0), dtype_code(r.dtype), w0.data_ptr(), bonus.data_ptr(), state.data_ptr(), out.data_ptr(),
+                                   batch.cu_q.data_ptr(), batch.state_slots.data_ptr(), batch.cu_q.numel() - 1, H, D, _stream()), "wkv_scan")
     return out

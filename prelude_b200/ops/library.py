@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 19
+ABI_VERSION = 20
 
 
 class KernelLibraryError(RuntimeError):
@@ -80,17 +80,25 @@ _SIGNATURES = {
     "pb_gemm_ref_batched": ([P, P, P, I, I, I, I, I, L, L, L, I, L, L, L, P], I),
     "pb_qkv_prepare": ([P, L, P, L, P, L, I, P, P, I, F, P, I, I, F, I, I, P, P, P, I, I, I, P, I, P, L, L, P, P, I, I, I, I, I, I, I,
                         I, I, P, P], I),
-    "pb_attention_paged": ([P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P], I),
+    "pb_attention_paged": ([P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, I, F, P, L, I, I, P, P], I),
     "pb_attention_paged_tc_supported": ([I, I, I, I, I], I),
     "pb_attention_paged_tc_tile_tokens": ([I, I], I),
     "pb_attention_paged_tc_scratch_floats": ([I, I, I, I], L),
-    "pb_attention_paged_tc_bf16": ([P, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, P, P], I),
+    "pb_attention_paged_tc_bf16": ([P, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, I, F, P, L, I, P, P, P], I),
     "pb_causal_conv_silu": ([P, L, P, P, P, P, I, P, P, P, P, I, I, I, P], I),
     "pb_conv_state_update": ([P, L, P, I, P, P, I, I, I, P], I),
     "pb_ssm_scan": ([P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P], I),
-    "pb_gated_group_rmsnorm": ([P, P, L, P, P, I, I, I, I, F, P], I),
+    "pb_gated_group_rmsnorm": ([P, P, L, P, P, I, I, I, I, F, I, P], I),
     "pb_scaled_sum": ([P, F, P, F, P, I, I, L, P], I),
     "pb_gemm_pair_grouped_bf16": ([P, P, P, I, I, I, I, L, L, L, I, P, P, P, I, I, P, P], I),
+    "pb_scaled_add_rmsnorm": ([P, I, L, F, P, P, I, I, P, P, I, I, F, P], I),
+    "pb_normed_pair_sum": ([P, P, F, P, P, F, F, P, I, I, I, P], I),
+    "pb_embed_gather_scaled": ([P, P, I, F, P, I, I, I, P], I),
+    "pb_tanh": ([P, P, I, L, P], I),
+    "pb_heads_prepare": ([P, L, P, L, P, L, I, P, P, F, P, I, I, P, P, L, F, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, P, P], I),
+    "pb_gated_delta_scan": ([P, L, P, L, P, L, I, P, P, P, P, P, P, I, I, I, I, I, P], I),
+    "pb_token_shift_mix": ([P, P, P, P, I, P, P, P, P, I, I, I, P], I),
+    "pb_wkv_scan": ([P, L, P, L, P, L, P, L, I, P, P, P, P, P, P, I, I, I, P], I),
 }
 
 _lock = threading.Lock()

@@ -32,9 +32,12 @@ def tc_takes(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[torch.Ten
 
 
 def attention_general(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[torch.Tensor], value_dim: int, batch, group: int,
-                      scale: float, window: Optional[int], sink: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      scale: float, window: Optional[int], sink: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+                      keep_first: int = 0, chunk: Optional[int] = None, softcap: Optional[float] = None,
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [T, H, kd] of the batch's tokens against the pages of cache group ``group``; ``v_pages`` None: the values are
-    the first ``value_dim`` elements of the key rows.  While a step is being captured piece by piece, the tensor-core
+    the first ``value_dim`` elements of the key rows.  ``keep_first``, ``chunk``, ``softcap``, ``gate``: as for
+    ``kernels.attention_paged``.  While a step is being captured piece by piece, the tensor-core
     kernel is launched between the pieces: its grid follows how the step's tokens are spread over requests."""
     T, H, kd = q.shape
     if out is None:
@@ -42,10 +45,12 @@ def attention_general(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[
     if not tc_takes(q, k_pages, v_pages, value_dim):
         # one warp per row whatever the step holds: the launch has the shape of the token count alone
         return K.attention_paged(q, k_pages, v_pages, value_dim, batch.positions, batch.table_row_of_token, batch.block_tables[group],
-                                 scale, window, sink, status=batch.status, out=out)
+                                 scale, window, sink, status=batch.status, out=out, keep_first=keep_first, chunk=chunk,
+                                 softcap=softcap, gate=gate)
     recorder = batch.extras.get("recorder")
     if recorder is not None and recorder.capturing and not batch.decode_only:
-        recorder.run_between_pieces(lambda: attention_general(q, k_pages, v_pages, value_dim, batch, group, scale, window, sink, out))
+        recorder.run_between_pieces(lambda: attention_general(q, k_pages, v_pages, value_dim, batch, group, scale, window, sink, out,
+                                                              keep_first, chunk, softcap, gate))
         return out
     lib = _l.library()
     table = batch.block_tables[group]
@@ -60,7 +65,9 @@ def attention_general(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[
     # few rows: deal each row's keys to several blocks, until the device is about twice full
     max_ctx = batch.max_kv_len if batch.max_kv_len else table.shape[1] * page_size
     if window:
-        max_ctx = min(max_ctx, window + batch.max_q_len + 32)
+        max_ctx = min(max_ctx, window + (keep_first or 0) + batch.max_q_len + 64)
+    elif chunk:
+        max_ctx = min(max_ctx, chunk + 32)
     blocks = n_tiles * G * (-(-(H // G) // 32))
     splits = 1
     if blocks < _sm_count(q.device):
@@ -75,5 +82,6 @@ def attention_general(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[
         q.data_ptr(), k_pages.data_ptr(), vp.data_ptr(), out.data_ptr(), K._ptr(sink), batch.positions.data_ptr(),
         batch.table_row_of_token.data_ptr(), table.data_ptr(), table.shape[1], batch.cu_q.data_ptr(), K._ptr(tile_seq), K._ptr(tile_tok0),
         n_tiles, page_size, num_pages, T, H, G, kd, value_dim, vp.shape[3], 1 if v_pages is None else 0, float(scale), int(window or 0),
+        int(keep_first or 0), int(chunk or 0), float(softcap or 0.0), K._ptr(gate), 0 if gate is None else gate.stride(0),
         splits, K._ptr(scratch), batch.status.data_ptr(), _l.current_stream_ptr(q.device)), "attention_paged_tc")
     return out

@@ -21,16 +21,25 @@ from .registry import RunContext, make_part, register_part
 
 @register_part("block", "prenorm_residual")
 class PreNormResidualBlock:
+    """The block of this file's head.  With ``residual_scale`` m other than 1 every sublayer's output joins the stream
+    times m (``kernels.Scaled``: the fused add multiplies while it adds, in float32); a block may then also have no
+    feed-forward, and hands on its mixer's output instead."""
+
     def __init__(self, spec: BlockSpec, prefix: str = ""):
         self.spec = spec
         p = spec.prefix
+        self.scale = float(spec.residual_scale)
+        if spec.feed_forward is None and spec.ff_norm is not None:
+            raise ValueError("a norm before a feed-forward that the block does not have")
         self.mixer_norm = make_part("norm", spec.mixer_norm, f"{p}.{spec.mixer_norm_name}")
         self.mixer = make_part("mixer", spec.mixer, f"{p}.{spec.mixer_name}")
-        self.ff_norm = make_part("norm", spec.ff_norm, f"{p}.{spec.ff_norm_name}")
-        self.feed_forward = make_part("feed_forward", spec.feed_forward, f"{p}.{spec.ff_name}")
+        self.ff_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.ff_norm = make_part("norm", spec.ff_norm, f"{p}.{spec.ff_norm_name}")
+            self.feed_forward = make_part("feed_forward", spec.feed_forward, f"{p}.{spec.ff_name}")
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward)
+        return tuple(x for x in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if x is not None)
 
     def tensors(self) -> Dict[str, TensorReq]:
         out: Dict[str, TensorReq] = {}
@@ -45,11 +54,19 @@ class PreNormResidualBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, delta: Optional[torch.Tensor], res: torch.Tensor, batch, cache, write_cache: bool) -> torch.Tensor:
+    def _out(self, y):
+        if self.scale == 1.0:
+            return y
+        from ..ops import kernels as K
+        return K.Scaled(y, self.scale)
+
+    def forward(self, delta, res: torch.Tensor, batch, cache, write_cache: bool):
         x = self.mixer_norm.add_forward(delta, res)
-        a = self.mixer.forward(x, batch, cache, write_cache)
+        a = self._out(self.mixer.forward(x, batch, cache, write_cache))
+        if self.feed_forward is None:
+            return a
         x = self.ff_norm.add_forward(a, res)
-        return self.feed_forward.forward(x)
+        return self._out(self.feed_forward.forward(x))
 
 
 @register_part("block", "sandwich_residual")

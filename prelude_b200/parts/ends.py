@@ -14,7 +14,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from ..config.spec import LinearHeadSpec, SinusoidEmbeddingSpec, TokenEmbeddingSpec
+from ..config.spec import LinearHeadSpec, ScaledEmbeddingSpec, SinusoidEmbeddingSpec, TokenEmbeddingSpec
 from ..ops import kernels as K
 from ..ops.linear import linear
 from ..weights.loader import TensorReq
@@ -55,6 +55,18 @@ class SinusoidTokenEmbedding(TokenEmbedding):
 
     def forward(self, batch) -> torch.Tensor:
         return K.embed_sinusoid(batch.token_ids, batch.positions, self.table, self.rate)
+
+
+@register_part("embedding", "token_embedding_scaled")
+class ScaledTokenEmbedding(TokenEmbedding):
+    """The token's row times a constant, multiplied in float32 as the row enters the residual stream.  The table
+    itself stays as stored, so a tied head reads it without the constant."""
+
+    def __init__(self, spec: ScaledEmbeddingSpec, prefix: str = ""):
+        super().__init__(spec, prefix)
+
+    def forward(self, batch) -> torch.Tensor:
+        return K.embed_gather_scaled(batch.token_ids, self.table, self.spec.scale)
 
 
 @register_part("head", "linear_head")

@@ -22,13 +22,16 @@ from . import block as _block  # noqa: F401
 from . import diff_attention as _diff_attention  # noqa: F401
 from . import ends as _ends  # noqa: F401
 from . import gqa as _gqa  # noqa: F401
+from . import gated_delta as _gated_delta  # noqa: F401
 from . import latent_attention as _latent_attention  # noqa: F401
+from . import masked_attention as _masked_attention  # noqa: F401
 from . import parallel as _parallel  # noqa: F401
 from . import state_space as _state_space  # noqa: F401
 from . import mlp as _mlp  # noqa: F401
 from . import moe as _moe  # noqa: F401
 from . import norm as _norm  # noqa: F401
 from . import rope as _rope  # noqa: F401
+from . import wkv as _wkv  # noqa: F401
 from .registry import KvPagesNeed, RunContext, RuntimeCaps, StateNeed, capturable, leaf_needs, make_part
 
 

@@ -9,7 +9,8 @@ is kept as ``offset + w``, added once in float32 when the tensor is loaded.
 
 What a norm adds to the residual stream may itself be waiting for a norm
 (``kernels.Normed``: the output of a sublayer that is normed before the add);
-the two norms and the add between them are then one kernel.
+the two norms and the add between them are then one kernel.  It may also join
+the stream times a constant (``kernels.Scaled``); the add multiplies then.
 """
 from __future__ import annotations
 
@@ -54,10 +55,14 @@ class RmsNorm:
         """res += x in place (float32), then the norm of res in the run's type."""
         if isinstance(x, K.Normed):
             return K.normed_add_rmsnorm(x, res, self.weight, self.spec.eps, self.dtype)
+        if isinstance(x, K.Scaled):
+            return K.scaled_add_rmsnorm(x, res, self.weight, self.spec.eps, self.dtype)
         return K.add_rmsnorm(x, res, self.weight, self.spec.eps, self.dtype)
 
     def gather_add_forward(self, x: Optional[torch.Tensor], res: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """norm(res[rows] + x[rows]) for the chosen rows only; res is left alone."""
         if isinstance(x, K.Normed):
             return K.normed_add_rmsnorm(x, res, self.weight, self.spec.eps, self.dtype, rows=rows)
+        if isinstance(x, K.Scaled):
+            return K.scaled_add_rmsnorm(x, res, self.weight, self.spec.eps, self.dtype, rows=rows)
         return K.gather_add_rmsnorm(x, res, rows, self.weight, self.spec.eps, self.dtype)

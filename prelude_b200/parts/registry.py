@@ -107,13 +107,17 @@ def capturable(part) -> bool:
 class KvPagesNeed:
     """A mixer that keeps keys and values of ``n_kv_heads`` x ``head_dim`` per
     token in pages; ``window`` set means only the last ``window`` tokens are
-    ever read again.  Where the values differ from the keys in head count or
+    ever read again, and beside them the first ``keep_first``; ``chunk`` set
+    means a token reads only keys of its own run of ``chunk`` positions, counted
+    from 0.  Where the values differ from the keys in head count or
     size, ``v_heads`` and ``v_head_dim`` say so (None: as the keys)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_heads: Optional[int] = None
     v_head_dim: Optional[int] = None
+    keep_first: int = 0
+    chunk: Optional[int] = None
 
     @property
     def value_heads(self) -> int:

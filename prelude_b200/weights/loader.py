@@ -43,10 +43,13 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+ANY = -1          # a dimension of a required shape that the file decides (the part reads it from the tensor)
+
+
 @dataclass(frozen=True)
 class TensorReq:
-    """What a part needs: the shape, and a role that tells the random-weights
-    writer how to fill it ("matrix", "norm", "bias")."""
+    """What a part needs: the shape (a dimension may be ``ANY``), and a role that tells
+    the random-weights writer how to fill it ("matrix", "norm", "bias", ...)."""
     shape: Tuple[int, ...]
     role: str = "matrix"
 
@@ -120,7 +123,7 @@ class WeightStore:
         for name, req in list(required.items()) + list(optional.items()):
             if name in have:
                 dtype, shape = self.info(name)
-                if tuple(shape) != tuple(req.shape):
+                if len(shape) != len(req.shape) or any(e != ANY and e != g for e, g in zip(req.shape, shape)):
                     wrong.append((name, tuple(req.shape), tuple(shape)))
                 if not dtype.is_floating_point:
                     wrong_type.append((name, str(dtype)))

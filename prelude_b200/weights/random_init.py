@@ -22,6 +22,7 @@ import torch
 
 from ..config.registry import load_model_config
 from ..parts.model import DecoderModel
+from .loader import ANY, TensorReq
 from .safetensors_io import write_safetensors
 
 
@@ -33,7 +34,7 @@ def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
 
 
 def random_tensors(config: Union[dict, object], seed: int = 0, std: float = 0.02, norm_jitter: float = 0.1,
-                   dtype: torch.dtype = torch.float32, device="cpu") -> Dict[str, torch.Tensor]:
+                   dtype: torch.dtype = torch.float32, device="cpu", free_dim: int = 16) -> Dict[str, torch.Tensor]:
     """Tensors by name for the model that ``config`` (a config.json dict or a
     typed configuration) describes.  With a CUDA ``device`` the numbers are drawn
     on the GPU (another stream of numbers than on the CPU): for benchmarks at
@@ -43,6 +44,8 @@ def random_tensors(config: Union[dict, object], seed: int = 0, std: float = 0.02
     out = {}
     for name, req in required.items():
         g = _generator(seed, name, device)
+        if ANY in req.shape:                # a size that only the tensors give: ``free_dim`` here
+            req = TensorReq(tuple(free_dim if d == ANY else d for d in req.shape), req.role)
         if req.role == "norm":
             t = 1.0 + (torch.rand(req.shape, generator=g, dtype=torch.float32, device=device) * 2.0 - 1.0) * norm_jitter
         elif req.role == "norm_zero":       # a scale stored around zero
@@ -51,6 +54,8 @@ def random_tensors(config: Union[dict, object], seed: int = 0, std: float = 0.02
             t = torch.randn(req.shape, generator=g, dtype=torch.float32, device=device) * (1.0 / max(1, req.shape[-1]) ** 0.5)
         elif req.role == "log_rate":        # logarithm of a decay rate: rates between about 0.4 and 2.7
             t = torch.rand(req.shape, generator=g, dtype=torch.float32, device=device) * 2.0 - 1.0
+        elif req.role == "blend":           # weights of a blend of two tokens, and other numbers between 0 and 1
+            t = torch.rand(req.shape, generator=g, dtype=torch.float32, device=device)
         elif req.role == "vector":          # a small vector whose products with its like enter an exponential
             t = torch.randn(req.shape, generator=g, dtype=torch.float32, device=device) * (0.5 / max(1, req.shape[0]) ** 0.5)
         else:
