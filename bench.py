@@ -26,7 +26,8 @@ requests, prompts of 128 to 2,048 tokens cut into portions of 512 beside the
 running decodes, 256 tokens each), as generated tokens a second by the wall clock.
 ``--workload pabelix`` and ``--workload kolisun`` put that design beside Qwen3 dense at equal
 layer sizes (random weights): prefill and decode steps, and the design's kernels beside their
-like, each a line of its own.  None of them changes the default run or its line.
+like, each a line of its own; ``--workload nedesun`` does so beside Kolisun and Qwen3 dense.
+None of them changes the default run or its line.
 """
 import argparse
 import json
@@ -663,6 +664,234 @@ def kolisun_compare(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --workload nedesun: the Nedesun design beside Kolisun (the closest design: attention beside a recurrent mixer, state
+# slots) and Qwen3 dense at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------------
+NEDESUN_SIZES = {
+    # width; attention (both kinds): heads, key/value heads, head size; window and kept first tokens; chunk; gated delta
+    # rule: heads, query/key heads, key and value sizes; time mixing: heads of 64; feed-forward width
+    "2k": dict(width=2048, heads=16, kv=4, dim=128, window=1024, keep=64, chunk=1024, d_heads=16, d_kv=8, d_dim=128, d_vdim=128,
+               w_dim=64, ff=8192),
+    "4k": dict(width=4096, heads=32, kv=8, dim=128, window=1024, keep=64, chunk=1024, d_heads=32, d_kv=16, d_dim=128, d_vdim=128,
+               w_dim=64, ff=12288),
+}
+
+
+def nedesun_config(z, layers, vocab):
+    """Layers that resemble a real model's: window attention beside the gated delta rule, then chunked attention with blended
+    values, then time mixing, and so on; every layer with a SiLU-gated feed-forward."""
+    par = {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                    "mask": {"size": z["window"], "keep_first": z["keep"]}},
+           "right": {"heads": z["d_heads"], "kv_heads": z["d_kv"], "dim": z["d_dim"], "vdim": z["d_vdim"], "conv": 4}}
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "mask": {"size": z["chunk"]}, "rot": {"dims": z["dim"], "base": 500000.0}, "softcap": 30.0, "v_mix": True}
+    wkv = {"heads": z["width"] // z["w_dim"], "dim": z["w_dim"]}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    kinds = [("parallel", par), ("attention", att), ("wkv", wkv)]
+    out = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": mlp} for i in range(layers)]
+    return {"architecture": "Nedesun", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "embedding": {"scale": 1.0}, "layers": out}
+
+
+def nedesun_kernels(pk, size):
+    """The new design's kernels beside their like of the closest model, one launch each: chunked, capped, gated attention
+    and window attention with kept first tokens and a sink beside Kolisun's window attention, over a prompt of 2,048 tokens
+    and for 8 decoded tokens; the kernel between projection and attention beside Kolisun's; the two recurrences and the
+    token blend beside Kolisun's state-space scan, against the bytes and operations they must do."""
+    import torch
+    from prelude_b200.cache.manager import CacheManager
+    from prelude_b200.engine.batch import StepItem, build_step_batch
+    from prelude_b200.ops import kernels as K
+    from prelude_b200.ops.attention import paged_attention
+    from prelude_b200.ops.paged_general import attention_general
+    from prelude_b200.parts.registry import CombinedNeed, KvPagesNeed, StateNeed
+    z, kz = NEDESUN_SIZES[size], KOLISUN_SIZES[size]
+    dev = torch.device("cuda:0")
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    out = {}
+    T, B = 2048, 8
+    H, G, D = z["heads"], z["kv"], z["dim"]
+    window, keep, chunk = z["window"], z["keep"], z["chunk"]
+    ctx = 2 * chunk - 1                                      # the decoded token is the last of its chunk
+    DH, DG, DD, DE = z["d_heads"], z["d_kv"], z["d_dim"], z["d_vdim"]
+    WH, WD = z["width"] // z["w_dim"], z["w_dim"]
+    SH, P, N, SG = kz["ss_heads"], kz["ss_dim"], kz["state"], kz["groups"]
+    d_channels, d_inner = 2 * DG * DD + DH * DE, DH * DE
+    s_inner, s_channels = SH * P, SH * P + 2 * SG * N
+    needs = [KvPagesNeed(G, D), KvPagesNeed(G, D),
+             CombinedNeed((StateNeed((DH, DD, DE), torch.float32), StateNeed((3, d_channels), None))),
+             CombinedNeed((StateNeed((WH, WD, WD), torch.float32), StateNeed((1, z["width"]), None))),
+             CombinedNeed((StateNeed((SH, N, P), torch.float32), StateNeed((3, s_channels), None)))]
+    cache = CacheManager(needs, PAGE_SIZE, (B * (ctx + 16) + T) // PAGE_SIZE + 8, B + 1, dev, bf)
+    gen, plain = cache.layer_cache(0), cache.layer_cache(1)
+    for lc in (gen, plain):
+        lc.k_pages.normal_()
+        lc.v_pages.normal_()
+    sink = torch.zeros(H, device=dev)
+    scale = D ** -0.5
+
+    def visible_pairs(n, first=0):
+        w = sum(min(i + 1, window) + max(0, min(keep, i + 1 - window)) for i in range(first, first + n))
+        c = sum(i % chunk + 1 for i in range(first, first + n))
+        return w, c
+
+    # -- one request of T prompt tokens
+    cache.add_request("p")
+    cache.grow("p", T)
+    batch = build_step_batch([StepItem("p", [0] * T, 0, [])], cache.block_tables(["p"]), [cache.slot_of("p")], dev, 10, 1 << 20)
+    cache.zero_fresh_state()
+    w_pairs, c_pairs = visible_pairs(T)
+    q = torch.randn(T, H, D, device=dev).to(bf)
+    gate = torch.randn(T, H, device=dev).to(bf)
+    g0 = cache.group_of[0]
+    ms = _event_ms(lambda: attention_general(q, gen.k_pages, gen.v_pages, D, batch, g0, scale, None, None, chunk=chunk, softcap=30.0, gate=gate),
+                   flush=flush)
+    out["prefill_attention"] = {"chunked_ms": round(ms, 4), "chunked_tflops": round(H * c_pairs * 4 * D / ms / 1e9, 1)}
+    ms = _event_ms(lambda: attention_general(q, gen.k_pages, gen.v_pages, D, batch, g0, scale, window, sink, keep_first=keep), flush=flush)
+    out["prefill_attention"].update(window_kept_ms=round(ms, 4), window_kept_tflops=round(H * w_pairs * 4 * D / ms / 1e9, 1))
+    k_pairs = sum(min(i + 1, kz["window"]) for i in range(T))
+    ms = _event_ms(lambda: paged_attention(q, plain.k_pages, plain.v_pages, batch, cache.group_of[1], scale, kz["window"]), flush=flush)
+    out["prefill_attention"].update(kolisun_window_ms=round(ms, 4), kolisun_window_tflops=round(H * k_pairs * 4 * D / ms / 1e9, 1))
+    # the kernel between projection and attention
+    proj = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+    rates = torch.rand(D // 2, device=dev)
+    qo = torch.empty(T, H, D, dtype=bf, device=dev)
+    v_first = torch.randn(T, G * D, device=dev).to(bf)
+    ms = _event_ms(lambda: K.heads_prepare(proj[:, :H * D], proj[:, H * D:(H + G) * D], proj[:, (H + G) * D:], n_heads=H, q_dim=D, rates=rates,
+                                           rot_dims=D, v_other=v_first, mix=0.3, positions=batch.positions,
+                                           table_row=batch.table_row_of_token, block_table=batch.block_tables[g0], q_out=qo,
+                                           k_pages=gen.k_pages, v_pages=gen.v_pages, status=batch.status), flush=flush)
+    moved = T * (H + 2 * G) * D * 2 * 2
+    out["projection_to_pages"] = {"rotate_blend_us": round(ms * 1e3, 2), "rotate_blend_gbs": round((moved + T * G * D * 2) / ms / 1e6, 1)}
+    hw = torch.ones(D, device=dev)
+    ms = _event_ms(lambda: K.heads_prepare(proj[:, :H * D], proj[:, H * D:(H + G) * D], proj[:, (H + G) * D:], n_heads=H, q_dim=D, q_weight=hw,
+                                           k_weight=hw, eps=1e-6, positions=batch.positions, table_row=batch.table_row_of_token,
+                                           block_table=batch.block_tables[g0], q_out=qo, k_pages=gen.k_pages, v_pages=gen.v_pages,
+                                           status=batch.status), flush=flush)
+    out["projection_to_pages"].update(head_norm_us=round(ms * 1e3, 2), head_norm_gbs=round(moved / ms / 1e6, 1))
+    wq, wk = torch.ones(H * D, device=dev), torch.ones(G * D, device=dev)
+    ms = _event_ms(lambda: K.qkv_prepare(proj[:, :H * D], proj[:, H * D:(H + G) * D], proj[:, (H + G) * D:], n_heads=H, q_dim=D, q_weight=wq,
+                                         k_weight=wk, k_norm_cols=G * D, eps=1e-6, rates=rates, rot_dims=D, adjacent=True,
+                                         positions=batch.positions, table_row=batch.table_row_of_token,
+                                         block_table=batch.block_tables[cache.group_of[1]], q_out=qo, k_pages=plain.k_pages,
+                                         v_pages=plain.v_pages, swizzle_k=True, swizzle_v=True, status=batch.status), flush=flush)
+    out["projection_to_pages"].update(kolisun_us=round(ms * 1e3, 2), kolisun_gbs=round(moved / ms / 1e6, 1))
+    # the recurrences over the prompt
+    dc, wc, sc = cache.layer_cache(2), cache.layer_cache(3), cache.layer_cache(4)
+    d_state, d_carried = dc.children[0].state, dc.children[1].state
+    dproj = (torch.randn(T, d_channels + d_inner + 2 * DH, device=dev) * 0.5).to(bf)
+    qkv, dgate = dproj[:, :d_channels], dproj[:, d_channels:d_channels + d_inner]
+    beta, a = dproj[:, d_channels + d_inner:d_channels + d_inner + DH], dproj[:, d_channels + d_inner + DH:]
+    d_conv = torch.randn(d_channels, 4, device=dev) * 0.5
+    al, hb, nw = torch.zeros(DH, device=dev), torch.zeros(DH, device=dev), torch.ones(d_inner, device=dev)
+    u = K.causal_conv_silu(qkv, d_conv, None, d_carried, batch)
+    y = K.gated_delta_scan(u, beta, a, al, hb, d_state, batch, DG)
+    ms_c = _event_ms(lambda: K.causal_conv_silu(qkv, d_conv, None, d_carried, batch, out=u), flush=flush)
+    ms_s = _event_ms(lambda: K.gated_delta_scan(u, beta, a, al, hb, d_state, batch, DG, out=y), flush=flush)
+    ms_n = _event_ms(lambda: K.gated_group_rmsnorm(y, dgate, nw, DH, 1e-6, gate_after=True), flush=flush)
+    out["gated_delta_prefill"] = {
+        "conv_us": round(ms_c * 1e3, 2), "conv_gbs": round(T * d_channels * 2 * 2 / ms_c / 1e6, 1),
+        "scan_us": round(ms_s * 1e3, 2), "scan_gbs": round((T * d_channels * 2 + T * d_inner * 4) / ms_s / 1e6, 1),
+        "scan_gflops": round(T * DH * DD * DE * 9 / ms_s / 1e6, 1),
+        "gated_norm_us": round(ms_n * 1e3, 2), "gated_norm_gbs": round(T * d_inner * (4 + 2 + 2) / ms_n / 1e6, 1)}
+    w_state, w_carried = wc.children[0].state, wc.children[1].state
+    w_inner = WH * WD
+    x = (torch.randn(T, z["width"], device=dev) * 0.5).to(bf)
+    mu = torch.rand(5, z["width"], device=dev)
+    blends = K.token_shift_mix(x, w_carried.view(w_carried.shape[0], z["width"]), mu, batch)
+    ms_b = _event_ms(lambda: K.token_shift_mix(x, w_carried.view(w_carried.shape[0], z["width"]), mu, batch, out=blends), flush=flush)
+    rkvw = (torch.randn(4, T, w_inner, device=dev) * 0.5).to(bf)
+    w0, bonus = torch.full((w_inner,), -1.0, device=dev), torch.zeros(w_inner, device=dev)
+    yw = K.wkv_scan(rkvw[0], rkvw[1], rkvw[2], rkvw[3], w0, bonus, w_state, batch)
+    ms_w = _event_ms(lambda: K.wkv_scan(rkvw[0], rkvw[1], rkvw[2], rkvw[3], w0, bonus, w_state, batch, out=yw), flush=flush)
+    out["time_mixing_prefill"] = {
+        "blend_us": round(ms_b * 1e3, 2), "blend_gbs": round(T * z["width"] * 2 * 6 / ms_b / 1e6, 1),
+        "scan_us": round(ms_w * 1e3, 2), "scan_gbs": round((4 * T * w_inner * 2 + T * w_inner * 4) / ms_w / 1e6, 1),
+        "scan_gflops": round(T * WH * WD * WD * 5 / ms_w / 1e6, 1)}
+    s_state, s_carried = sc.children[0].state, sc.children[1].state
+    sproj = (torch.randn(T, 2 * s_inner + 2 * SG * N + SH, device=dev) * 0.5).to(bf)
+    xbc, dt = sproj[:, s_inner:s_inner + s_channels], sproj[:, s_inner + s_channels:]
+    s_conv, s_b = torch.randn(s_channels, 4, device=dev) * 0.5, torch.zeros(s_channels, device=dev)
+    shb, sal, sdd = torch.zeros(SH, device=dev), torch.zeros(SH, device=dev), torch.ones(SH, device=dev)
+    su = K.causal_conv_silu(xbc, s_conv, s_b, s_carried, batch)
+    sy = K.ssm_scan(su, dt, shb, sal, sdd, s_state, batch, SG)
+    ms_k = _event_ms(lambda: K.ssm_scan(su, dt, shb, sal, sdd, s_state, batch, SG, out=sy), flush=flush)
+    out["kolisun_state_space_prefill"] = {"scan_us": round(ms_k * 1e3, 2),
+                                          "scan_gbs": round((T * s_channels * 2 + T * s_inner * 4) / ms_k / 1e6, 1),
+                                          "scan_gflops": round(T * SH * N * P * 6 / ms_k / 1e6, 1)}
+    cache.release("p")
+    # -- B single tokens at ctx keys
+    rids = [f"d{i}" for i in range(B)]
+    for r in rids:
+        cache.add_request(r)
+        cache.grow(r, ctx + 1)
+    batch = build_step_batch([StepItem(r, [0], ctx, []) for r in rids], cache.block_tables(rids), [cache.slot_of(r) for r in rids], dev, 10, 1 << 20)
+    cache.zero_fresh_state()
+    q = torch.randn(B, H, D, device=dev).to(bf)
+    gate = torch.randn(B, H, device=dev).to(bf)
+    row_bytes = G * 2 * D * 2
+    ms = _event_ms(lambda: attention_general(q, gen.k_pages, gen.v_pages, D, batch, g0, scale, None, None, chunk=chunk, softcap=30.0, gate=gate),
+                   flush=flush, reps=20)
+    out["decode_attention"] = {"chunked_us": round(ms * 1e3, 2), "chunked_gbs": round(B * chunk * row_bytes / ms / 1e6, 1)}
+    ms = _event_ms(lambda: attention_general(q, gen.k_pages, gen.v_pages, D, batch, g0, scale, window, sink, keep_first=keep), flush=flush, reps=20)
+    out["decode_attention"].update(window_kept_us=round(ms * 1e3, 2), window_kept_gbs=round(B * (window + keep) * row_bytes / ms / 1e6, 1))
+    ms = _event_ms(lambda: paged_attention(q, plain.k_pages, plain.v_pages, batch, cache.group_of[1], scale, kz["window"]), flush=flush, reps=20)
+    out["decode_attention"].update(kolisun_window_us=round(ms * 1e3, 2), kolisun_window_gbs=round(B * kz["window"] * row_bytes / ms / 1e6, 1))
+    ms = _event_ms(lambda: K.gated_delta_scan(u[:B], beta[:B], a[:B], al, hb, d_state, batch, DG, out=y[:B]), flush=flush, reps=20)
+    out["gated_delta_decode"] = {"scan_us": round(ms * 1e3, 2), "scan_state_gbs": round(B * DH * DD * DE * 4 * 2 / ms / 1e6, 1)}
+    ms = _event_ms(lambda: K.wkv_scan(rkvw[0, :B], rkvw[1, :B], rkvw[2, :B], rkvw[3, :B], w0, bonus, w_state, batch, out=yw[:B]), flush=flush, reps=20)
+    out["time_mixing_decode"] = {"scan_us": round(ms * 1e3, 2), "scan_state_gbs": round(B * WH * WD * WD * 4 * 2 / ms / 1e6, 1)}
+    ms = _event_ms(lambda: K.ssm_scan(su[:B], dt[:B], shb, sal, sdd, s_state, batch, SG, out=sy[:B]), flush=flush, reps=20)
+    out["kolisun_state_space_decode"] = {"scan_us": round(ms * 1e3, 2), "scan_state_gbs": round(B * SH * N * P * 4 * 2 / ms / 1e6, 1)}
+    out["peaks"] = {"bf16_tflops": pk["bf16_tflops"], "hbm_gbs": pk["hbm_gbs"], "source": pk["source"]}
+    return out
+
+
+def nedesun_compare(args):
+    """Prefill and decode throughput of Nedesun beside Kolisun and Qwen3 dense at equal layer sizes (random weights,
+    bfloat16): one prompt of --prefill-tokens through the step function, and --batch requests decoding behind
+    --prefix-len tokens on the captured step, both timed on the device.  One JSON line of its own."""
+    import torch
+    pk = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    t_begin = time.time()
+    points = []
+    vocab = 32768
+    for size in args.sizes.split(","):
+        z = NEDESUN_SIZES[size]
+        layers = args.layers or 6
+        arms = {
+            "nedesun": nedesun_config(z, layers, vocab),
+            "kolisun": kolisun_config(KOLISUN_SIZES[size], layers, vocab),
+            "qwen3": dict(QWEN3_4B, vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
+                          num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["dim"], tie_word_embeddings=True),
+        }
+        point = {"size": size, "layers": layers, "width": z["width"]}
+        for name, cfg in arms.items():
+            pages_per_req = -(-(PREFIX_LEN + args.warmup + args.steps + 2) // PAGE_SIZE)
+            engine = _engine_for(cfg, args.batch * pages_per_req + 2 * (PREFILL_TOKENS // PAGE_SIZE) + 8, args.batch + 2)
+            shim = {"vocab_size": vocab}
+            prefill_ms, _ = time_prefill(engine, shim, args.warmup)
+            dec, _ = time_decode(engine, shim, args.batch, args.steps, args.warmup, seed=1)
+            point[name] = {"prefill_tok_s": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                           "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms_per_step"], 4),
+                           "weight_gb": round(engine.model.weight_bytes() / 1e9, 3)}
+            del engine
+            torch.cuda.empty_cache()
+        point["kernels"] = nedesun_kernels(pk, size)
+        points.append(point)
+    clocks.stop()
+    print(json.dumps({"metric": "Nedesun beside Kolisun and Qwen3 dense at equal layer sizes: prefill and decode tokens a second, device-timed",
+                      "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": args.steps,
+                      "warmup": args.warmup, "config": {"batch": args.batch, "prefix_len": PREFIX_LEN, "prefill_tokens": PREFILL_TOKENS,
+                                                        "page_size": PAGE_SIZE, "l2": "inputs_exceed_l2 (steps), flushed (kernels)"},
+                      "points": points, "clocks": clocks.summary([(t_begin, time.time())])}))
+    return 0
+
+
 def serve(args):
     """A mixed continuous batch through ``Engine.generate`` (host tokens in, host tokens out): ``--requests`` prompts
     of uniform random ids with lengths uniform in [128, 2048], prompts cut into portions of ``--prefill-chunk``
@@ -727,10 +956,11 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels' timeline of one layer of the decode step to stderr (needs PRELUDE_TIMELINE=1 in the environment)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "pabelix", "kolisun"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "pabelix", "kolisun", "nedesun"],
                     help="serving: a mixed continuous batch through Engine.generate instead of the decode step (a line of its own); "
-                         "pabelix, kolisun: that design beside Qwen3 dense at equal layer sizes (a line of its own)")
-    ap.add_argument("--sizes", default="2k,4k", help="pabelix, kolisun: which layer sizes to run (2k, 4k)")
+                         "pabelix, kolisun: that design beside Qwen3 dense at equal layer sizes (a line of its own); "
+                         "nedesun: that design beside Kolisun and Qwen3 dense at equal layer sizes (a line of its own)")
+    ap.add_argument("--sizes", default="2k,4k", help="pabelix, kolisun, nedesun: which layer sizes to run (2k, 4k)")
     ap.add_argument("--requests", type=int, default=32, help="serving: number of requests")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: tokens per portion of a prompt")
     ap.add_argument("--new-tokens", type=int, default=256, help="serving: generated tokens per request")
@@ -761,6 +991,9 @@ def main():
     if args.workload == "kolisun":
         args.layers = 0 if args.layers == MODEL["num_hidden_layers"] else args.layers
         return kolisun_compare(args)
+    if args.workload == "nedesun":
+        args.layers = 0 if args.layers == MODEL["num_hidden_layers"] else args.layers
+        return nedesun_compare(args)
     import torch
     pk = peaks()
     # cache: the largest point (64 requests) with room for prefix + generated tokens, in whole pages
