@@ -55,6 +55,13 @@ struct PtParams {
     int tok;                        // tokens of a block: 256 / group
     int q_rows;                     // rows of a query box: min(tok, 128)
     int kv_rows;                    // rows of a key/value box: min(page_size, 128)
+    // options of the masked attention (all off for the plain entry point)
+    int keep_first;                 // positions below it stay visible behind a window
+    int chunk;                      // > 0: a query sees its own run of `chunk` positions only (counted from 0)
+    float cap_in, cap_out;          // capped scores: s <- cap_out * tanh(s * cap_in), in the units of q . k (cap_in = 0: off)
+    const float* sink;              // [n_heads] or null: exp(sink) joins the denominator
+    const __nv_bfloat16* gate;      // [n_tokens, n_heads] rows ld_gate apart, or null: sigmoid(gate) multiplies the head's output
+    long long ld_gate;
 };
 
 template <int D>
@@ -79,16 +86,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int q_base = p.cu_q[r], q_len = p.cu_q[r + 1] - q_base, pos0 = p.q_start[r];
     const int n_tok = min(TOK, q_len - tok0);                    // tokens of this block
     const int p_min = pos0 + tok0, p_max = p_min + n_tok - 1;
-    const int lo = p.window > 0 ? max(0, p_min - p.window + 1) : 0;
+    const int lo = p.window > 0 ? max(0, p_min - p.window + 1) : (pp.chunk > 0 ? p_min - p_min % pp.chunk : 0);
     const int kt0 = lo / PT_KEYS;
     const int lo_run = lo / pp.kv_rows * pp.kv_rows;             // first key of the first run that holds a visible key
+    // Kept first tokens: the key tiles wholly before the window that hold some of them come first (tile j of the block
+    // is key tile j for j < keep_tiles, key tile kt0 + j - keep_tiles after them); kept keys inside the window's own
+    // tiles need no tile of their own.
+    const int keep = p.window > 0 ? pp.keep_first : 0;
+    const int keep_tiles = min((keep + PT_KEYS - 1) / PT_KEYS, kt0);
+    const int keep_hi_run = keep > 0 ? (keep - 1) / pp.kv_rows * pp.kv_rows : 0;   // the last run that holds a kept key
+    auto key_tile = [&](int j) { return j < keep_tiles ? j : kt0 + j - keep_tiles; };
     // key tiles of each row tile: row tile m holds tokens (m * 128) % TOK .. ; with one head per block
     // (TOK = 256) the second row tile holds the later 128 tokens and may be empty
     int n_m[2];
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
         const int tl_first = (m * 128) % TOK, tl_last = min(tl_first + min(TOK, 128), n_tok) - 1;
-        n_m[m] = tl_first < n_tok ? (pos0 + tok0 + tl_last) / PT_KEYS - kt0 + 1 : 0;
+        n_m[m] = tl_first < n_tok ? (pos0 + tok0 + tl_last) / PT_KEYS - kt0 + 1 + keep_tiles : 0;
     }
     const int n_tiles = max(n_m[0], n_m[1]);
 
@@ -114,14 +128,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int runs = PT_KEYS / pp.kv_rows;
         const int last_pi = p_max / ps;                          // the last page the block reads; the request holds it for sure
         const int hi_run = p_max / pp.kv_rows * pp.kv_rows;      // first key of the last run that holds a visible key
-        int win_pi = (kt0 * PT_KEYS) / ps;                       // table index that lane 0 of `cur` holds
+        int win_pi = (key_tile(0) * PT_KEYS) / ps;               // table index that lane 0 of `cur` holds
         int cur = table[min(win_pi + lane, last_pi)], nxt = table[min(win_pi + 32 + lane, last_pi)];
         // The page and the row in it where the u-th run of key tile j starts.  Runs without a visible key (before the
         // window, after the last key) are read from the nearest run that has one: their probabilities are zero, and
         // the value rows are cleared by the softmax threads.
+        // A run with kept keys is read as it is (their pages stay held); in a tile of kept keys the runs after them
+        // repeat the last of them (the pages between the kept keys and the window may have been given back).
         auto locate = [&](int j, int u, int& page, int& row) {
-            int j0 = (kt0 + j) * PT_KEYS + u * pp.kv_rows;
-            j0 = min(max(j0, lo_run), hi_run);
+            const int kt = key_tile(j);
+            int j0 = kt * PT_KEYS + u * pp.kv_rows;
+            if (kt < kt0) j0 = min(j0, keep_hi_run);
+            else j0 = min(j0 < keep ? j0 : max(j0, lo_run), hi_run);
             const int pi = j0 / ps;
             row = j0 - pi * ps;
             const int idx = pi - win_pi;                         // 0 .. 47: the tile starts inside `cur` and spans at most 16 pages
@@ -151,7 +169,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int j = 0; j < n_tiles; ++j) {
             unsigned char* sK = sKV + stage * 2 * T::TILE_BYTES;
             unsigned char* sV = sK + T::TILE_BYTES;
-            while (((kt0 + j) * PT_KEYS) / ps - win_pi >= 32) {  // slide the window of table entries
+            const int want_pi = (key_tile(j) * PT_KEYS) / ps;
+            if (want_pi - win_pi >= 64) {                         // from the kept keys to the window: start anew
+                win_pi = want_pi;
+                cur = table[min(win_pi + lane, last_pi)];
+                nxt = table[min(win_pi + 32 + lane, last_pi)];
+            }
+            while (want_pi - win_pi >= 32) {                      // slide the window of table entries
                 cur = nxt;
                 win_pi += 32;
                 nxt = table[min(win_pi + 32 + lane, last_pi)];
@@ -248,7 +272,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int hg = R / TOK, tl = R - hg * TOK;
         const bool valid = tl < n_tok;
         const int row_pos = pos0 + tok0 + min(tl, n_tok - 1);      // rows without a token behave like the last token
-        const int row_lo = p.window > 0 ? row_pos - p.window + 1 : 0;
+        const int row_lo = p.window > 0 ? row_pos - p.window + 1 : (pp.chunk > 0 ? row_pos - row_pos % pp.chunk : 0);
+        const float cap2 = pp.cap_in * 2.8853900817779268f;       // 2 log2(e) / cap, in the units of q . k
         const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_addr = lane_base + m * PT_S_COLS, o_addr = lane_base + T::O_COL + m * D;
         float m_ref = -INFINITY, l = 0.f;
@@ -262,12 +287,35 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int c = 0; c < PT_KEYS; c += 32) tc_tmem_ld32(s_addr + c, sr + c);
             tc_tmem_ld_wait();
-            const int key0 = (kt0 + j) * PT_KEYS;
+            const int key0 = key_tile(j) * PT_KEYS;
+            if (pp.cap_in > 0.f) {                                 // capped scores, before the mask
+                float am[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < PT_KEYS; ++c) am[c & 3] = fmaxf(am[c & 3], fabsf(__uint_as_float(sr[c])));
+                if (fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])) * pp.cap_in < 0.5f) {
+                    // Every score of the row's tile is well under the cap (the usual case): tanh(x) / x as a polynomial in
+                    // x^2 on the multiply-add units; the next term is below 5e-6 at 0.5.  The special-function unit, which
+                    // the exponentials keep busy, stays out of it.
+#pragma unroll
+                    for (int c = 0; c < PT_KEYS; ++c) {
+                        const float s0 = __uint_as_float(sr[c]), x = s0 * pp.cap_in, x2 = x * x;
+                        const float t = fmaf(x2, fmaf(x2, fmaf(x2, fmaf(x2, 0.021869488536155203f, -0.053968253968253971f), 0.13333333333333333f),
+                                                      -0.33333333333333333f), 1.0f);
+                        sr[c] = __float_as_uint(s0 * t);
+                    }
+                } else {                                           // tanh(x) = 1 - 2 / (exp(2 x) + 1)
+#pragma unroll
+                    for (int c = 0; c < PT_KEYS; ++c) {
+                        const float e = ex2_approx(fminf(__uint_as_float(sr[c]) * cap2, 80.0f));
+                        sr[c] = __float_as_uint(pp.cap_out * (1.0f - __fdividef(2.0f, e + 1.0f)));
+                    }
+                }
+            }
             if (key0 + PT_KEYS - 1 > row_pos || key0 < row_lo) {
 #pragma unroll
                 for (int c = 0; c < PT_KEYS; ++c) {
                     const int kj = key0 + c;
-                    if (kj > row_pos || kj < row_lo) sr[c] = __float_as_uint(-INFINITY);
+                    if (kj > row_pos || (kj < row_lo && kj >= keep)) sr[c] = __float_as_uint(-INFINITY);
                 }
             }
             // eight chains side by side: one chain of 128 dependent operations would take their latency 128 times
@@ -314,7 +362,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // Value rows of keys that nobody may see (before the first visible run, after the last key) hold whatever
             // their page holds, and 0 x NaN is NaN: this group clears them once the tile has landed and before it
             // lets its product start.  Only the first and the last tile of the block have such rows.
-            const int clear_below = j == 0 ? lo_run - key0 : 0, clear_from = j == n_tiles - 1 ? p_max + 1 - key0 : PT_KEYS;
+            // (With kept first tokens every run before the window is either theirs or a copy of a run that is read: nothing to clear.)
+            const int clear_below = (j == 0 && keep == 0) ? lo_run - key0 : 0, clear_from = j == n_tiles - 1 ? p_max + 1 - key0 : PT_KEYS;
             if (clear_below > 0 || clear_from < PT_KEYS) {
                 const int stage = j % S;
                 ok = mbar_wait_bounded(&v_full[stage], (j / S) & 1);
@@ -336,7 +385,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (ok) ok = mbar_wait_bounded(&o_full[m], 0);
             if (__all_sync(0xffffffffu, ok)) {
                 tc_fence_after();
-                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                const int head = kvh * G + hg;
+                if (pp.sink != nullptr && m_ref != -INFINITY) l += ex2_approx(fmaf(pp.sink[head], 1.4426950408889634f, -m_ref));
+                float inv = l > 0.f ? 1.0f / l : 0.f;
+                if (pp.gate != nullptr && valid)
+                    inv *= 1.0f / (1.0f + __expf(-__bfloat162float(pp.gate[(size_t)(q_base + tok0 + tl) * pp.ld_gate + head])));
                 __nv_bfloat16* dst = p.out + ((size_t)(q_base + tok0 + (valid ? tl : 0)) * p.n_heads + kvh * G + hg) * D;
 #pragma unroll 1
                 for (int c = 0; c < D; c += 32) {
@@ -411,17 +464,51 @@ PB_API int pb_attention_prefill_tc_supported(int n_heads, int n_kv_heads, int he
     return 1;
 }
 
+// The same for pages whose rows are stored as they are: the copies into shared memory permute them (128-byte swizzle of
+// the tensor maps), which puts the same bytes in the same places as a plain copy of permuted pages.
+PB_API int pb_attention_prefill_tc_plain_pages_supported(int n_heads, int n_kv_heads, int head_dim, int page_size) {
+    return pb_attention_prefill_tc_supported(n_heads, n_kv_heads, head_dim, page_size, 1);
+}
+
 // Tokens of one tile of the host's list for this kernel.
 PB_API int pb_attention_prefill_tc_tile_tokens(int n_heads, int n_kv_heads) { return 256 / (n_heads / n_kv_heads); }
 
 // Tiles are listed by the host: tile t covers tokens tile_tok0[t] .. of request tile_seq[t]'s portion,
 // 256 / (n_heads / n_kv_heads) tokens each.  q and out are dense [n_tokens, n_heads, head_dim].
+//
+// The masked entry point adds: keep_first (positions below it stay visible behind the window), chunk (> 0: a query sees
+// its own run of `chunk` positions only; not together with a window), softcap (> 0: score <- softcap * tanh(score /
+// softcap) after the scale), sink (float32 [n_heads] or null), gate ([n_tokens, n_heads] bfloat16, rows ld_gate apart, or
+// null).  swizzle = 0: pages whose rows are stored as they are.
+PB_API int pb_attention_prefill_tc_masked_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                               const int32_t* block_table, int table_stride, const int32_t* positions,
+                                               const int32_t* token_seq, const int32_t* cu_q, const int32_t* q_start,
+                                               const int32_t* tile_seq, const int32_t* tile_tok0, int n_tiles, int page_size,
+                                               int num_pages, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                               float scale, int window, int swizzle, int keep_first, int chunk, float softcap,
+                                               const float* sink, const void* gate, long long ld_gate, int* status,
+                                               cudaStream_t stream);
+
 PB_API int pb_attention_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
                                         const int32_t* block_table, int table_stride, const int32_t* positions,
                                         const int32_t* token_seq, const int32_t* cu_q, const int32_t* q_start,
                                         const int32_t* tile_seq, const int32_t* tile_tok0, int n_tiles, int page_size,
                                         int num_pages, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                         float scale, int window, int swizzle, int* status, cudaStream_t stream) {
+    PB_REQUIRE(swizzle, "attention_prefill_tc: this entry point takes permuted pages");
+    return pb_attention_prefill_tc_masked_bf16(q, k_pages, v_pages, out, block_table, table_stride, positions, token_seq, cu_q, q_start,
+                                               tile_seq, tile_tok0, n_tiles, page_size, num_pages, n_tokens, n_heads, n_kv_heads,
+                                               head_dim, scale, window, swizzle, 0, 0, 0.f, nullptr, nullptr, 0, status, stream);
+}
+
+PB_API int pb_attention_prefill_tc_masked_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                               const int32_t* block_table, int table_stride, const int32_t* positions,
+                                               const int32_t* token_seq, const int32_t* cu_q, const int32_t* q_start,
+                                               const int32_t* tile_seq, const int32_t* tile_tok0, int n_tiles, int page_size,
+                                               int num_pages, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                               float scale, int window, int swizzle, int keep_first, int chunk, float softcap,
+                                               const float* sink, const void* gate, long long ld_gate, int* status,
+                                               cudaStream_t stream) {
     PtParams pp{};
     AttnParams& p = pp.a;
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
@@ -431,7 +518,11 @@ PB_API int pb_attention_prefill_tc_bf16(const void* q, const void* k_pages, cons
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.swizzle = swizzle;
     if (int e = attn_check_common("attention_prefill_tc", p)) return e;
-    PB_REQUIRE(pb_attention_prefill_tc_supported(n_heads, n_kv_heads, head_dim, page_size, swizzle),
+    PB_REQUIRE(keep_first >= 0 && chunk >= 0 && !(window > 0 && chunk > 0) && softcap >= 0.f && (gate == nullptr || ld_gate >= n_heads),
+               "attention_prefill_tc: window %d, kept %d, chunk %d, cap %g", window, keep_first, chunk, (double)softcap);
+    pp.keep_first = window > 0 ? keep_first : 0; pp.chunk = chunk; pp.sink = sink; pp.gate = (const __nv_bfloat16*)gate; pp.ld_gate = ld_gate;
+    pp.cap_in = softcap > 0.f ? scale / softcap : 0.f; pp.cap_out = softcap > 0.f ? softcap / scale : 0.f;
+    PB_REQUIRE(pb_attention_prefill_tc_supported(n_heads, n_kv_heads, head_dim, page_size, 1),
                "attention_prefill_tc: n_heads=%d n_kv_heads=%d head_dim=%d page_size=%d swizzle=%d not taken (permuted pages, "
                "head_dim 64 or 128, a power of two of query heads per key/value head, page_size dividing or divided by 128)",
                n_heads, n_kv_heads, head_dim, page_size, swizzle);
@@ -456,8 +547,9 @@ PB_API int pb_attention_prefill_tc_bf16(const void* q, const void* k_pages, cons
         cuuint64_t dims[5] = {64, (cuuint64_t)head_dim / 64, (cuuint64_t)page_size, (cuuint64_t)n_kv_heads, (cuuint64_t)num_pages};
         cuuint64_t strides[4] = {128, row, row * page_size, row * page_size * n_kv_heads};
         cuuint32_t box[5] = {64, 1, (cuuint32_t)pp.kv_rows, 1, 1};
-        if (int e = pt_encode(&mk, k_pages, 5, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "the key pages")) return e;
-        if (int e = pt_encode(&mv, v_pages, 5, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "the value pages")) return e;
+        const CUtensorMapSwizzle how = swizzle ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B;
+        if (int e = pt_encode(&mk, k_pages, 5, dims, strides, box, how, "the key pages")) return e;
+        if (int e = pt_encode(&mv, v_pages, 5, dims, strides, box, how, "the value pages")) return e;
     }
     int e = head_dim == 64 ? pt_launch<64>(mq, mk, mv, pp, n_tiles, stream) : pt_launch<128>(mq, mk, mv, pp, n_tiles, stream);
     if (e) return e;

@@ -22,6 +22,8 @@
 
 #include <math.h>
 
+#include <type_traits>
+
 namespace {
 
 #define GD_COLS 16
@@ -31,7 +33,7 @@ __device__ __forceinline__ float gd_softplus(float x) { return x > 20.0f ? x : l
 
 template <typename T, int NPL>
 __global__ void __launch_bounds__(256)
-gated_delta_scan_kernel(const T* __restrict__ u, long long ld_u, const T* __restrict__ b_in, long long ld_b, const T* __restrict__ a_in,
+gated_delta_scan_kernel(const T* __restrict__ u_in, long long ld_u, const T* __restrict__ b_in, long long ld_b, const T* __restrict__ a_in,
                         long long ld_a, const float* __restrict__ a_log, const float* __restrict__ dt_bias, float* __restrict__ state,
                         float* __restrict__ y, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ slots, int H, int G, int D,
                         int E) {
@@ -70,40 +72,58 @@ gated_delta_scan_kernel(const T* __restrict__ u, long long ld_u, const T* __rest
             for (int idx = lt; idx < 2 * BUF; idx += 128) sm[idx] = 0.f;
         __syncthreads();
     }
-    auto load_chunk = [&](int k) {
+    // A loading warp has CHUNK / 4 tokens of a chunk: it asks for all their rows before it works on the first, so the
+    // trips to memory overlap (a token past the chunk's end repeats the last one's addresses and is dropped).  A chunk of
+    // at most four tokens, a decode step's, is one token a warp.
+    auto load_tokens = [&](int k, auto per_warp) {
+        constexpr int TPW = decltype(per_warp)::value;
         float* buf = sm + (k & 1) * BUF;
         const int t0 = k * CHUNK, cnt = min(CHUNK, n_tok - t0);
-        for (int tt = lw; tt < cnt; tt += 4) {                   // a warp per token
-            const size_t t = (size_t)(first + t0 + tt);
-            const T* row = u + t * ld_u;
+        float qv[TPW][NPL / 4], kv[TPW][NPL / 4], vv[TPW], braw[TPW], araw[TPW];      // NPAD / 32 elements of q and k a lane
+#pragma unroll
+        for (int u = 0; u < TPW; ++u) {
+            const int tt = lw + 4 * u;
+            const size_t t = (size_t)(first + t0 + min(tt, cnt - 1));
+            const T* row = u_in + t * ld_u;
             const T* qr = row + (size_t)g * D;
             const T* kr = row + (size_t)(G + g) * D;
-            float qv[NPL / 4], kv[NPL / 4];                      // NPAD / 32 elements a lane
-            float sq = 0.f, sk = 0.f;
 #pragma unroll
             for (int i = 0; i < NPL / 4; ++i) {
                 const int n = lane + 32 * i;
-                qv[i] = n < D ? pb_ld(qr + n) : 0.f;
-                kv[i] = n < D ? pb_ld(kr + n) : 0.f;
-                sq = fmaf(qv[i], qv[i], sq);
-                sk = fmaf(kv[i], kv[i], sk);
+                qv[u][i] = n < D ? pb_ld(qr + n) : 0.f;
+                kv[u][i] = n < D ? pb_ld(kr + n) : 0.f;
             }
-            const float vv = (lane < GD_COLS && p_first + lane < E) ? pb_ld(row + (size_t)2 * G * D + (size_t)h * E + p_first + lane) : 0.f;
-            float braw = 0.f, araw = 0.f;
-            if (lane == 0) { braw = pb_ld(b_in + t * ld_b + h); araw = pb_ld(a_in + t * ld_a + h); }
+            vv[u] = (lane < GD_COLS && p_first + lane < E) ? pb_ld(row + (size_t)2 * G * D + (size_t)h * E + p_first + lane) : 0.f;
+            braw[u] = araw[u] = 0.f;
+            if (lane == 0) { braw[u] = pb_ld(b_in + t * ld_b + h); araw[u] = pb_ld(a_in + t * ld_a + h); }
+        }
+#pragma unroll
+        for (int u = 0; u < TPW; ++u) {
+            const int tt = lw + 4 * u;
+            if (tt >= cnt) break;
+            float sq = 0.f, sk = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPL / 4; ++i) {
+                sq = fmaf(qv[u][i], qv[u][i], sq);
+                sk = fmaf(kv[u][i], kv[u][i], sk);
+            }
             const float iq = q_scale / sqrtf(pb_warp_sum(sq) + 1e-6f), ik = 1.0f / sqrtf(pb_warp_sum(sk) + 1e-6f);
             float* dst = buf + tt * TOK;
 #pragma unroll
             for (int i = 0; i < NPL / 4; ++i) {
                 const int n = lane + 32 * i;
-                if (n < D) { dst[n] = kv[i] * ik; dst[NPAD + n] = qv[i] * iq; }
+                if (n < D) { dst[n] = kv[u][i] * ik; dst[NPAD + n] = qv[u][i] * iq; }
             }
-            if (lane < GD_COLS) dst[2 * NPAD + lane] = vv;
+            if (lane < GD_COLS) dst[2 * NPAD + lane] = vv[u];
             if (lane == 0) {
-                dst[2 * NPAD + GD_COLS] = 1.0f / (1.0f + expf(-braw));
-                dst[2 * NPAD + GD_COLS + 1] = expf(-rate * gd_softplus(araw + bias));
+                dst[2 * NPAD + GD_COLS] = 1.0f / (1.0f + expf(-braw[u]));
+                dst[2 * NPAD + GD_COLS + 1] = expf(-rate * gd_softplus(araw[u] + bias));
             }
         }
+    };
+    auto load_chunk = [&](int k) {
+        if (n_tok - k * CHUNK <= 4) load_tokens(k, std::integral_constant<int, 1>{});
+        else load_tokens(k, std::integral_constant<int, CHUNK / 4>{});
     };
     if (!computes) load_chunk(0);
     __syncthreads();

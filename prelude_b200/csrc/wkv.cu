@@ -21,6 +21,8 @@
 
 #include <math.h>
 
+#include <type_traits>
+
 namespace {
 
 #define WKV_COLS 16
@@ -93,35 +95,50 @@ wkv_scan_kernel(const T* __restrict__ r_in, long long ld_r, const T* __restrict_
             for (int idx = lt; idx < 2 * BUF; idx += 128) sm[idx] = 0.f;
         __syncthreads();
     }
-    auto load_chunk = [&](int k) {
+    // A loading warp has CHUNK / 4 tokens of a chunk: it asks for all their rows before it works on the first, so the
+    // trips to memory overlap (a token past the chunk's end repeats the last one's addresses and is dropped).  A chunk of
+    // at most four tokens, a decode step's, is one token a warp.
+    auto load_tokens = [&](int k, auto per_warp) {
+        constexpr int TPW = decltype(per_warp)::value;
         float* buf = sm + (k & 1) * BUF;
         const int t0 = k * CHUNK, cnt = min(CHUNK, n_tok - t0);
-        for (int tt = lw; tt < cnt; tt += 4) {                   // a warp per token
-            const size_t t = (size_t)(first + t0 + tt);
+        float rv[TPW][NPL / 4], kv[TPW][NPL / 4], wv[TPW][NPL / 4], vv[TPW];
+#pragma unroll
+        for (int u = 0; u < TPW; ++u) {
+            const int tt = lw + 4 * u;
+            const size_t t = (size_t)(first + t0 + min(tt, cnt - 1));
             const T* rr = r_in + t * ld_r + (size_t)h * D;
             const T* kr = k_in + t * ld_k + (size_t)h * D;
             const T* wr = w_in + t * ld_w + (size_t)h * D;
-            float rv[NPL / 4], kv[NPL / 4], wv[NPL / 4];
 #pragma unroll
             for (int i = 0; i < NPL / 4; ++i) {
                 const int n = lane + 32 * i;
-                rv[i] = n < D ? pb_ld(rr + n) : 0.f;
-                kv[i] = n < D ? pb_ld(kr + n) : 0.f;
-                wv[i] = n < D ? pb_ld(wr + n) : 0.f;
+                rv[u][i] = n < D ? pb_ld(rr + n) : 0.f;
+                kv[u][i] = n < D ? pb_ld(kr + n) : 0.f;
+                wv[u][i] = n < D ? pb_ld(wr + n) : 0.f;
             }
-            const float vv = (lane < WKV_COLS && p_first + lane < D) ? pb_ld(v_in + t * ld_v + (size_t)h * D + p_first + lane) : 0.f;
+            vv[u] = (lane < WKV_COLS && p_first + lane < D) ? pb_ld(v_in + t * ld_v + (size_t)h * D + p_first + lane) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < TPW; ++u) {
+            const int tt = lw + 4 * u;
+            if (tt >= cnt) break;
             float ruk = 0.f;
             float* dst = buf + tt * TOK;
 #pragma unroll
             for (int i = 0; i < NPL / 4; ++i) {
                 const int n = lane + 32 * i;
-                ruk = fmaf(rv[i] * uv[i], kv[i], ruk);
-                if (n < D) { dst[n] = rv[i]; dst[NPAD + n] = kv[i]; dst[2 * NPAD + n] = expf(-expf(wv[i] + w0v[i])); }
+                ruk = fmaf(rv[u][i] * uv[i], kv[u][i], ruk);
+                if (n < D) { dst[n] = rv[u][i]; dst[NPAD + n] = kv[u][i]; dst[2 * NPAD + n] = expf(-expf(wv[u][i] + w0v[i])); }
             }
             ruk = pb_warp_sum(ruk);
-            if (lane < WKV_COLS) dst[3 * NPAD + lane] = vv;
+            if (lane < WKV_COLS) dst[3 * NPAD + lane] = vv[u];
             if (lane == 0) dst[3 * NPAD + WKV_COLS] = ruk;
         }
+    };
+    auto load_chunk = [&](int k) {
+        if (n_tok - k * CHUNK <= 4) load_tokens(k, std::integral_constant<int, 1>{});
+        else load_tokens(k, std::integral_constant<int, CHUNK / 4>{});
     };
     if (!computes) load_chunk(0);
     __syncthreads();

@@ -44,6 +44,8 @@ _SIGNATURES = {
     "pb_attention_prefill_tc_supported": ([I, I, I, I, I], I),
     "pb_attention_prefill_tc_tile_tokens": ([I, I], I),
     "pb_attention_prefill_tc_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P], I),
+    "pb_attention_prefill_tc_plain_pages_supported": ([I, I, I, I], I),
+    "pb_attention_prefill_tc_masked_bf16": ([P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, F, P, P, L, P, P], I),
     "pb_attention_decode_scratch_floats": ([I, I, I, I], L),
     "pb_attention_decode_blocks_per_sm": ([I], I),
     "pb_attention_decode_bf16": ([P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, I, P, P, P, P], I),

@@ -4,7 +4,10 @@ never what is computed.
 
 float32 always runs the plain warp-per-row kernel.  bfloat16 runs the tensor-core kernel where it takes the shape
 (key size in multiples of 16, value size in multiples of 32 up to 512), prompt portions and single tokens alike; a
-step of few rows has its keys dealt to several blocks per row (PRELUDE_GENERAL_ATTN=plain turns it off).
+step of few rows has its keys dealt to several blocks per row (PRELUDE_GENERAL_ATTN=plain turns it off).  Prompt
+portions that fill the tcgen05 prompt kernel's blocks go to that kernel where it takes the shape (keys and values of
+one size, 64 or 128, in pages of their own; PRELUDE_GENERAL_PROMPT_ATTN=mma turns it off): it knows the same masks,
+cap, sink and gate and reads the same pages, permuting them on their way into shared memory.
 """
 from __future__ import annotations
 
@@ -15,10 +18,11 @@ import torch
 
 from . import kernels as K
 from . import library as _l
-from .attention import _prefill_plan, _sm_count
+from .attention import TC_MIN_FILL, _prefill_plan, _sm_count
 from .library import check
 
 KERNEL = os.environ.get("PRELUDE_GENERAL_ATTN", "auto")
+PROMPT_KERNEL = os.environ.get("PRELUDE_GENERAL_PROMPT_ATTN", "auto")
 MAX_SPLITS = 32
 
 
@@ -59,7 +63,24 @@ def attention_general(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[
         tile_seq = tile_tok0 = None
         n_tiles = T
     else:
-        tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, lib.pb_attention_paged_tc_tile_tokens(H, G))
+        # The tcgen05 prompt kernel works on 256 query rows at a time and pays for all of them: it takes the portions
+        # that fill at least TC_MIN_FILL of a block's tokens, this kernel the shorter ones and the single tokens.  Both
+        # write disjoint rows of `out`.
+        long_min, long_tiles = None, 0
+        if (PROMPT_KERNEL != "mma" and v_pages is not None and kd == value_dim and v_pages.shape[3] == kd
+                and lib.pb_attention_prefill_tc_plain_pages_supported(H, G, kd, page_size)):
+            tc_tokens = lib.pb_attention_prefill_tc_tile_tokens(H, G)
+            long_min = 1 if PROMPT_KERNEL == "tc" else max(2, int(tc_tokens * TC_MIN_FILL))
+            tile_seq, tile_tok0, long_tiles = _prefill_plan(batch, tc_tokens, long_min, None)
+            if long_tiles:
+                check(lib.pb_attention_prefill_tc_masked_bf16(
+                    q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), table.data_ptr(), table.shape[1],
+                    batch.positions.data_ptr(), batch.table_row_of_token.data_ptr(), batch.cu_q.data_ptr(), batch.q_start.data_ptr(),
+                    tile_seq.data_ptr(), tile_tok0.data_ptr(), long_tiles, page_size, num_pages, T, H, G, kd, float(scale), int(window or 0), 0,
+                    int(keep_first or 0), int(chunk or 0), float(softcap or 0.0), K._ptr(sink), K._ptr(gate),
+                    0 if gate is None else gate.stride(0), batch.status.data_ptr(), _l.current_stream_ptr(q.device)),
+                    "attention_prefill_tc_masked")
+        tile_seq, tile_tok0, n_tiles = _prefill_plan(batch, lib.pb_attention_paged_tc_tile_tokens(H, G), 0, long_min)
         if n_tiles == 0:
             return out
     # few rows: deal each row's keys to several blocks, until the device is about twice full
@@ -70,9 +91,10 @@ def attention_general(q: torch.Tensor, k_pages: torch.Tensor, v_pages: Optional[
         max_ctx = min(max_ctx, chunk + 32)
     blocks = n_tiles * G * (-(-(H // G) // 32))
     splits = 1
-    if blocks < _sm_count(q.device):
+    # (putting the parts together writes every row of the step: not beside rows that the prompt kernel wrote)
+    if blocks < _sm_count(q.device) and (batch.decode_only or not long_tiles):
         key_tiles = -(-max_ctx // 32)
-        splits = max(1, min(MAX_SPLITS, -(-2 * _sm_count(q.device) // blocks), key_tiles))
+        splits = max(1, min(MAX_SPLITS, 2 * _sm_count(q.device) // blocks, key_tiles))    # two blocks a multiprocessor: one wave
         splits = -(-key_tiles // -(-key_tiles // splits))               # as many blocks as have tiles to work on
     scratch = None
     if splits > 1:

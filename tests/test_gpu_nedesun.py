@@ -521,3 +521,59 @@ def test_command_line_generates_from_a_nedesun_folder(folders):
     for _ in range(5):
         seq.append(int(plain.forward(cfg, w, seq, torch.float64)[-1].argmax()))
     assert json.loads(out.stdout.strip().splitlines()[0])["token_ids"] == seq[4:]
+
+
+# -- the tcgen05 prompt kernel with masks, cap, sink and gate against the general kernel -------------------------------------
+@pytest.mark.parametrize("heads,kv,dim,page,window,keep,chunk,cap,sink,gate", [
+    (8, 2, 128, 16, 300, 40, None, None, True, False), (8, 2, 128, 16, None, 0, 200, 30.0, False, True), (4, 4, 64, 16, 100, 0, None, None, True, False),
+    (16, 2, 64, 32, None, 0, 128, 5.0, False, True), (4, 1, 128, 16, 129, 130, None, None, False, False), (8, 8, 128, 128, 50, 7, None, 8.0, True, True),
+    (2, 1, 64, 8, None, 0, 1000, None, False, False), (8, 2, 128, 16, 700, 300, None, None, True, False), (32, 1, 64, 16, None, 0, 77, 20.0, True, True),
+    (8, 2, 128, 64, 256, 128, None, None, True, False), (4, 2, 128, 16, None, 0, None, 12.0, True, True)])
+def test_prompt_kernel_with_masks_equals_the_general_kernel(heads, kv, dim, page, window, keep, chunk, cap, sink, gate):
+    """Random keys and values in scattered pages; requests of unequal length: a long prompt from position 0, a portion far
+    into a long context whose pages behind the window (but for the kept first tokens) and behind the chunk were given
+    back, a portion that starts inside a key tile, a short one.  Both kernels read the same pages."""
+    from prelude_b200.cache.manager import CacheManager
+    from prelude_b200.engine.batch import StepItem, build_step_batch
+    from prelude_b200.ops import paged_general as G
+    from prelude_b200.parts.registry import KvPagesNeed
+    dev = torch.device(DEV)
+    g = torch.Generator().manual_seed(heads * 31 + dim + (window or 0) + (chunk or 0))
+    need = KvPagesNeed(kv, dim, window, v_heads=kv, v_head_dim=dim, keep_first=keep if window else 0, chunk=chunk)
+    shape = [(0, 700), (1900, 300), (333, 150), (64, 40), (5, 2)]
+    cache = CacheManager([need], page, sum(-(-(a + b) // page) for a, b in shape) + 3, 8, dev, torch.bfloat16)
+    items, slots = [], []
+    for i, (have, new) in enumerate(shape):
+        cache.add_request(i)
+        if have:
+            cache.grow(i, have)
+            cache.trim(i)                                  # as after the step that brought the tokens before
+        cache.grow(i, have + new)
+        items.append(StepItem(i, [0] * new, have, []))
+        slots.append(cache.slot_of(i))
+    cache.check()
+    lc = cache.layer_cache(0)
+    lc.k_pages.copy_(torch.randn(lc.k_pages.shape, generator=g).to(dev, torch.bfloat16))
+    lc.v_pages.copy_(torch.randn(lc.v_pages.shape, generator=g).to(dev, torch.bfloat16))
+    batch = build_step_batch(items, cache.block_tables(list(range(len(shape)))), slots, dev, 10, 1 << 20)
+    if window or chunk:
+        assert int((batch.block_tables[0][1][:100] < 0).sum()) > 0          # pages were given back
+    q = (torch.randn(batch.n_tokens, heads, dim, generator=g) * 1.5).to(dev, torch.bfloat16)
+    sinks = torch.linspace(-1.0, 3.0, heads).to(dev) if sink else None
+    gates = torch.randn(batch.n_tokens, heads + 3, generator=g).to(dev, torch.bfloat16)[:, :heads] if gate else None
+    scale = 1.0 / math.sqrt(dim)
+    assert G._l.library().pb_attention_prefill_tc_plain_pages_supported(heads, kv, dim, page)
+    old = G.PROMPT_KERNEL
+    try:
+        G.PROMPT_KERNEL = "mma"
+        want = G.attention_general(q, lc.k_pages, lc.v_pages, dim, batch, 0, scale, window, sinks, keep_first=keep, chunk=chunk, softcap=cap,
+                                   gate=gates).float().clone()
+        G.PROMPT_KERNEL = "auto"
+        got = G.attention_general(q, lc.k_pages, lc.v_pages, dim, batch, 0, scale, window, sinks, keep_first=keep, chunk=chunk, softcap=cap,
+                                  gate=gates).float()
+    finally:
+        G.PROMPT_KERNEL = old
+    assert int(batch.status.item()) == 0
+    err = (got - want).abs()
+    assert float(err.max()) < 4e-2 * float(want.abs().max()) and float(err.mean()) < 4e-3 * float(want.abs().max()), \
+        (float(err.max()), float(err.mean()), float(want.abs().max()), int(err.max(dim=-1).values.max(dim=-1).values.argmax()))
