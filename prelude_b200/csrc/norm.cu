@@ -59,9 +59,10 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, int n_parts, size_t
 
 // Four elements per thread and access, the row kept in registers between the
 // two passes.  width % 4 == 0, width <= 4 * blockDim * ITERS.
-template <typename TX, typename TY, int ITERS>
+// SCALED: what is added is xs times the parts' sum (taken on its own, in ascending order), as one fused multiply-add.
+template <typename TX, typename TY, int ITERS, bool SCALED = false>
 __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, size_t part_stride, float* __restrict__ res,
-                                        const float* __restrict__ w, TY* __restrict__ y, int width, float eps) {
+                                        const float* __restrict__ w, TY* __restrict__ y, int width, float eps, float xs) {
     pb_grid_dep_launch();
     PB_TL(PB_TL_NORM, PB_TL_ENTRY);
     __shared__ float red[32];
@@ -109,16 +110,17 @@ __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, s
         if (i < n4) {
             float4 v = keep[it];
             if (x != nullptr) {
+                float4 acc = SCALED ? make_float4(0.f, 0.f, 0.f, 0.f) : v;
                 const TX* xr = x + row * width + 4 * (size_t)i;
                 if constexpr (sizeof(TX) == 2) {
                     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[it]);
                     float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-                    v.x += a.x; v.y += a.y; v.z += b.x; v.w += b.y;
+                    acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
                 } else if (ahead) {
                     // the parts in ascending order
 #pragma unroll
                     for (int u = 0; u < 4; ++u)
-                        if (u < n_parts) { v.x += part[it][u].x; v.y += part[it][u].y; v.z += part[it][u].z; v.w += part[it][u].w; }
+                        if (u < n_parts) { acc.x += part[it][u].x; acc.y += part[it][u].y; acc.z += part[it][u].z; acc.w += part[it][u].w; }
                 } else {
                     // the parts in ascending order, four loads in flight at a time
                     for (int s0 = 0; s0 < n_parts; s0 += 4) {
@@ -129,9 +131,11 @@ __global__ void add_rmsnorm_vec4_kernel(const TX* __restrict__ x, int n_parts, s
                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                         for (int u = 0; u < 4; ++u)
-                            if (s0 + u < n_parts) { v.x += a[u].x; v.y += a[u].y; v.z += a[u].z; v.w += a[u].w; }
+                            if (s0 + u < n_parts) { acc.x += a[u].x; acc.y += a[u].y; acc.z += a[u].z; acc.w += a[u].w; }
                     }
                 }
+                if constexpr (SCALED) v = make_float4(fmaf(xs, acc.x, v.x), fmaf(xs, acc.y, v.y), fmaf(xs, acc.z, v.z), fmaf(xs, acc.w, v.w));
+                else v = acc;
                 r4[i] = v;
             }
             keep[it] = v;
@@ -177,11 +181,11 @@ static int launch_add_rmsnorm(const void* x, int n_parts, size_t part_stride, fl
     if (vec) {
         int iters = (width / 4 + threads - 1) / threads;
         if (iters <= 2)
-            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 2>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 2>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps, 1.0f);
         else if (iters <= 4)
-            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 4>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 4>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps, 1.0f);
         else
-            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 8>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps);
+            pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 8>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps, 1.0f);
     } else {
         pb_launch(add_rmsnorm_kernel<TX, TY>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps);
     }
@@ -540,6 +544,24 @@ __global__ void scaled_add_rmsnorm_kernel(const TX* __restrict__ x, int n_parts,
     }
 }
 
+// The whole-step form on the vectorised kernel; false: the shape or the alignment is not taken.
+template <typename TX, typename TY>
+static bool launch_scaled_add_rmsnorm_vec4(const void* x, int n_parts, size_t part_stride, float xs, float* res, const float* w, void* y,
+                                           int rows, int width, float eps, cudaStream_t stream) {
+    const int threads = norm_threads(width);
+    const bool vec = width % 4 == 0 && pb_aligned(res, 16) && pb_aligned(w, 16) && pb_aligned(y, 8 * sizeof(TY) / 2) &&
+                     pb_aligned(x, 8 * sizeof(TX) / 2) && part_stride % 4 == 0 && width <= 4 * threads * 8;
+    if (!vec) return false;
+    const int iters = (width / 4 + threads - 1) / threads;
+    if (iters <= 2)
+        pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 2, true>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps, xs);
+    else if (iters <= 4)
+        pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 4, true>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps, xs);
+    else
+        pb_launch(add_rmsnorm_vec4_kernel<TX, TY, 8, true>, dim3(rows), dim3(threads), 0, stream, (const TX*)x, n_parts, part_stride, res, w, (TY*)y, width, eps, xs);
+    return true;
+}
+
 PB_API int pb_scaled_add_rmsnorm(const void* x, int x_parts, long long part_stride, float scale, float* res, const int32_t* rows,
                                  int n_out, int n_rows_total, const float* w, void* y, int dtype, int width, float eps,
                                  cudaStream_t stream) {
@@ -549,6 +571,18 @@ PB_API int pb_scaled_add_rmsnorm(const void* x, int x_parts, long long part_stri
                "scaled_add_rmsnorm: %d parts %lld apart", x_parts, part_stride);
     PB_REQUIRE(rows != nullptr || n_out == n_rows_total, "scaled_add_rmsnorm: without chosen rows every row is made");
     if (n_out == 0) return 0;
+    if (rows == nullptr) {
+        bool done = false;
+        if (x_parts > 0) {
+            PB_DISPATCH_DTYPE(dtype, T, (done = launch_scaled_add_rmsnorm_vec4<float, T>(x, x_parts, (size_t)part_stride, scale, res, w, y, n_out, width, eps, stream)));
+        } else {
+            PB_DISPATCH_DTYPE(dtype, T, (done = launch_scaled_add_rmsnorm_vec4<T, T>(x, 1, (size_t)0, scale, res, w, y, n_out, width, eps, stream)));
+        }
+        if (done) {
+            PB_CHECK_LAUNCH("scaled_add_rmsnorm");
+            return 0;
+        }
+    }
     if (x_parts > 0) {
         PB_DISPATCH_DTYPE(dtype, T,
             (pb_launch(scaled_add_rmsnorm_kernel<float, T>, dim3(n_out), dim3(norm_threads(width)), 0, stream, (const float*)x, x_parts,
