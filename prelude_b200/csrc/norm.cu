@@ -609,13 +609,15 @@ __global__ void normed_pair_sum_kernel(const T* __restrict__ a, const float* __r
     const T* ar = a + row * width;
     const T* br = b + row * width;
     float ssa = 0.f, ssb = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+#pragma unroll 8
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {          // several rounds' loads in flight together
         const float va = pb_ld(ar + i), vb = pb_ld(br + i);
         ssa += va * va;
         ssb += vb * vb;
     }
     const float ta = block_sum(ssa, red), tb = block_sum(ssb, red);
     const float ia = sa / sqrtf(ta / (float)width + eps), ib = sb / sqrtf(tb / (float)width + eps);
+#pragma unroll 8
     for (int i = threadIdx.x; i < width; i += blockDim.x)
         out[row * width + i] = pb_ld(ar + i) * ia * wa[i] + pb_ld(br + i) * ib * wb[i];
 }
