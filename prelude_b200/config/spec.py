@@ -234,7 +234,9 @@ class ValueBlendSpec:
 @dataclass(frozen=True)
 class MaskedAttentionSpec:
     """Grouped-query softmax attention over a paged cache whose options are per head: an RMS norm of every q head and
-    every k head over its own elements with one scale shared by all heads (``head_norm_eps``), a rotation of the
+    every k head over its own elements with one scale shared by all heads (``head_norm_eps``; ``head_norm_scale``
+    False: no learned scale; ``head_norm_after_rotation``: the rotated head is normed instead of the head being
+    normed and then rotated, which differs where the rotation's amplitude is not 1), a rotation of the
     first ``position.dims`` elements of every head (or none), and one of two masks.  ``window``: position i sees j
     with 0 <= i - j < window, and also every j < ``keep_first``.  ``chunk``: i sees j <= i only inside its own run
     of ``chunk`` positions, counted from position 0.  ``softcap``: score <- softcap * tanh(score / softcap) after
@@ -251,6 +253,8 @@ class MaskedAttentionSpec:
     qkv_bias: bool = False
     o_bias: bool = False
     head_norm_eps: Optional[float] = None
+    head_norm_scale: bool = True
+    head_norm_after_rotation: bool = False
     window: Optional[int] = None
     keep_first: int = 0
     chunk: Optional[int] = None
@@ -330,6 +334,29 @@ class WkvSpec:
 
 
 @dataclass(frozen=True)
+class DecayedLinearAttentionSpec:
+    """Linear attention with a decaying matrix state per head and a decay that is a constant of the model.
+    q = silu(W_q x) and k = silu(W_k x) are ``num_heads`` x ``head_dim``, v = silu(W_v x) is ``num_heads`` x
+    ``value_dim``.  Per head S_t = decays[h] S_(t-1) + k_t v_t^T and o_t = S_t^T q_t, with no other scale.  The
+    concatenated heads are brought to unit root mean square together (``norm_eps``), times a learned scale over all
+    of them, times sigmoid(W_g x), and projected out.  The state [head_dim, value_dim] (float32) is carried per
+    sequence."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    value_dim: int
+    decays: Tuple[float, ...]
+    norm_eps: float
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    gate_name: str = "g"
+    norm_name: str = "norm"
+    o_name: str = "o"
+    kind: str = "decayed_linear_attention"
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec:
     """Several mixers side by side on the same input; the result is the sum of their outputs, each times its
     scale.  ``names[i]`` is mixer i's prefix below this mixer's.  With ``member_norms`` every member's output is
@@ -361,7 +388,10 @@ class RoutedExpertsSpec:
     scores are sigmoid(W_router x) in 32-bit.  Experts form ``n_groups`` equal runs of neighbours; a group's
     score is the sum of its ``group_score_top`` largest scores, and only experts of the ``keep_groups`` best
     groups can be chosen.  The chosen experts' outputs are added up weighted by their scores
-    (``renormalize``: divided by the scores' sum first).  Expert e's tensors are ``<prefix>.<expert_prefix><e>.<name>``."""
+    (``renormalize``: divided by the scores' sum first).  With ``correction_name`` a learned number per expert
+    (``<prefix>.<correction_name>``) is added to the scores wherever they decide the choice (group scores and the
+    experts chosen; the sums may be negative, and an expert outside the kept groups counts as minus infinity); the
+    weights stay the scores without it.  Expert e's tensors are ``<prefix>.<expert_prefix><e>.<name>``."""
     hidden_size: int
     expert_size: int
     n_experts: int
@@ -370,6 +400,7 @@ class RoutedExpertsSpec:
     keep_groups: int = 1
     group_score_top: int = 2
     renormalize: bool = False
+    correction_name: Optional[str] = None
     router_name: str = "router"
     expert_prefix: str = "e"
     gate_name: str = "gate"
@@ -380,7 +411,7 @@ class RoutedExpertsSpec:
 
 @dataclass(frozen=True)
 class GatedMlpSpec:
-    """down(act(gate(x)) * up(x)), no biases."""
+    """down(act(gate(x)) * up(x)), no biases; ``activation``: "silu", or "gelu_tanh" (the tanh form of GELU)."""
     hidden_size: int
     intermediate_size: int
     activation: str = "silu"

@@ -46,6 +46,10 @@ __device__ __forceinline__ float pb_warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+// the tanh form of GELU: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), in float32
+__device__ __forceinline__ float pb_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
 __device__ __forceinline__ float pb_warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -6,7 +6,9 @@
 //   route    scores s = sigmoid(z) of float32 router logits; experts form `groups` equal runs of neighbours, a
 //            group's score is the sum of its `gtop` largest scores, only experts of the `keep` best groups can
 //            be chosen; the `top` largest allowed scores are chosen (ties: the smaller index), their weights are
-//            the scores themselves (or, with `renorm`, divided by their sum).
+//            the scores themselves (or, with `renorm`, divided by their sum).  With a `correction` per expert the
+//            choice (group scores and the chosen experts) goes by s + correction, which may be negative; the
+//            weights stay the scores s without it.
 //   sort     slot i = token * top + choice.  The slots are grouped by expert: offsets[e] .. offsets[e + 1] are the
 //            places of expert e, order[place] = slot, place_of[slot] = place, and the places are cut into row
 //            tiles of MOE_BM that never span two experts (tile_expert, tile_row0; -1 behind the last tile).
@@ -85,9 +87,9 @@ __device__ __forceinline__ void moe_warp_argmax(float& val, int& idx) {
     }
 }
 
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top,
-                                                        int groups, int keep, int gtop, int renorm, int32_t* __restrict__ ids,
-                                                        float* __restrict__ weights) {
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                                                        int n_tokens, int n_experts, int top, int groups, int keep, int gtop,
+                                                        int renorm, int32_t* __restrict__ ids, float* __restrict__ weights) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     const int lane = threadIdx.x & 31;
@@ -96,11 +98,12 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     const float* z = logits + (size_t)t * n_experts;
     const int per = n_experts / groups;
     const int slots = (n_experts + 31) / 32;                 // experts per lane, 32 at most
-    float sc[32];
+    const float NONE = -INFINITY;                            // below every choice score, negative ones included
+    float sc[32];                                            // what the choice goes by
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         const int e = lane + 32 * i;
-        sc[i] = (i < slots && e < n_experts) ? 1.0f / (1.0f + expf(-z[e])) : -1.0f;
+        sc[i] = (i < slots && e < n_experts) ? 1.0f / (1.0f + expf(-z[e])) + (correction ? correction[e] : 0.f) : NONE;
     }
     unsigned long long allowed = groups >= 64 ? ~0ull : ((1ull << groups) - 1ull);
     if (keep < groups) {
@@ -110,7 +113,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
             float sum = 0.f;
             const int n = min(gtop, per);
             for (int r = 0; r < n; ++r) {
-                float val = -1.0f;
+                float val = NONE;
                 int idx = 0x7fffffff;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -118,7 +121,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
                     if (i < slots && e < n_experts && e / per == g && !((taken >> i) & 1u) && sc[i] > val) { val = sc[i]; idx = e; }
                 }
                 moe_warp_argmax(val, idx);
-                sum += fmaxf(val, 0.f);
+                if (idx < n_experts) sum += val;
                 if (idx < n_experts && (idx & 31) == lane) taken |= 1u << (idx >> 5);
             }
             gscore[g] = sum;
@@ -137,7 +140,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     int my_id = 0;
     float my_w = 0.f, total = 0.f;
     for (int r = 0; r < top; ++r) {
-        float val = -1.0f;
+        float val = NONE;
         int idx = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -148,8 +151,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
         if (idx >= n_experts) {                              // scores that are no numbers: any allowed expert not yet chosen
             idx = 0;
             val = 0.f;
-        } else if ((idx & 31) == lane) {
-            chosen |= 1u << (idx >> 5);
+        } else {
+            if ((idx & 31) == lane) chosen |= 1u << (idx >> 5);
+            if (correction) val = 1.0f / (1.0f + expf(-z[idx]));          // the weight is the score without the correction
         }
         total += val;
         if (lane == r) { my_id = idx; my_w = val; }
@@ -160,8 +164,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     }
 }
 
-PB_API int pb_moe_route(const float* logits, int n_tokens, int n_experts, int top, int groups, int keep, int gtop, int renorm,
-                        int32_t* ids, float* weights, cudaStream_t stream) {
+// correction: float32 [n_experts] added to the scores for the choice only, or null.
+PB_API int pb_moe_route(const float* logits, const float* correction, int n_tokens, int n_experts, int top, int groups, int keep,
+                        int gtop, int renorm, int32_t* ids, float* weights, cudaStream_t stream) {
     PB_REQUIRE(n_tokens >= 0 && n_experts > 0 && n_experts <= MOE_MAX_EXPERTS && top > 0 && top <= MOE_MAX_TOP,
                "moe_route: bad sizes T=%d E=%d top=%d", n_tokens, n_experts, top);
     PB_REQUIRE(groups > 0 && groups <= MOE_MAX_GROUPS && n_experts % groups == 0 && keep > 0 && keep <= groups && gtop > 0 &&
@@ -169,8 +174,8 @@ PB_API int pb_moe_route(const float* logits, int n_tokens, int n_experts, int to
     PB_REQUIRE(top <= keep * (n_experts / groups), "moe_route: top=%d experts cannot come from %d groups of %d", top, keep, n_experts / groups);
     PB_REQUIRE(logits && ids && weights, "moe_route: null pointer");
     if (n_tokens == 0) return 0;
-    pb_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, n_tokens, n_experts, top, groups, keep, gtop,
-              renorm, ids, weights);
+    pb_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, correction, n_tokens, n_experts, top, groups,
+              keep, gtop, renorm, ids, weights);
     PB_CHECK_LAUNCH("moe_route");
     return 0;
 }

@@ -6,6 +6,8 @@
 //   pb_ssm_scan             dt = softplus(dt + bias); S <- exp(-exp(A_log) dt) S + dt B x^T; y = S^T C + D x, token by
 //                           token, the state [heads, state, head_dim] float32 per sequence, read at the start and written
 //                           at the end of the step
+//   pb_decay_scan           the same recurrence with a constant decay per head and no step size: linear attention with a
+//                           decaying state, S <- decay S + k v^T; o = S^T q, q, k, v the SiLU of the projection's columns
 //   pb_gated_group_rmsnorm  y * silu(z), brought to unit root mean square in equal parts, times a scale; or, with the gate
 //                           after the norm, y brought to unit root mean square in equal parts, times a scale, times silu(z)
 //
@@ -156,9 +158,14 @@ __global__ void conv_state_update_kernel(const T* __restrict__ in, long long ld_
 #define SCAN_COLS 16
 #define SCAN_LANES 8
 
-template <typename T, int NPL>
+//
+// FIXED: the same recurrence with a decay per head that is a constant of the model and no step size (linear attention
+// with a decaying state: S <- decay_h S + k v^T, o = S^T q).  x, B, C are then v, k, q read straight from the
+// projection's columns (rows `ld_u` apart) and passed through SiLU by the loaders, in float32; dt is 1, D is 0, and
+// `a_log` holds the decays themselves.
+template <typename T, int NPL, bool FIXED>
 __global__ void __launch_bounds__(256)
-ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long ld_dt, const float* __restrict__ dt_bias,
+ssm_scan_kernel(const T* __restrict__ u, long long ld_u, const T* __restrict__ dt_in, long long ld_dt, const float* __restrict__ dt_bias,
                 const float* __restrict__ a_log, const float* __restrict__ d_skip, float* __restrict__ state,
                 float* __restrict__ y, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ slots, int heads, int P,
                 int N, int groups) {
@@ -172,7 +179,8 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
     const int r = blockIdx.y;
     const int tid = threadIdx.x;
     const bool computes = tid < SCAN_COLS * SCAN_LANES;
-    const float neg_a = -expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];     // written by no kernel: before the wait
+    // written by no kernel: before the wait
+    const float neg_a = FIXED ? a_log[h] : -expf(a_log[h]), bias = FIXED ? 0.f : dt_bias[h], skip = FIXED ? 0.f : d_skip[h];
     pb_grid_dep_wait();
     const int first = cu_q[r], n_tok = cu_q[r + 1] - first;
     if (n_tok <= 0) return;
@@ -194,7 +202,8 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
     // load threads
     const int lt = tid - SCAN_COLS * SCAN_LANES;
     constexpr int VN = 16 / sizeof(T);                                            // elements of a 16-byte load
-    const bool vec = N % VN == 0 && channels % VN == 0 && inner % VN == 0 && pb_aligned_dev(u, 16);
+    const bool vec = N % VN == 0 && channels % VN == 0 && inner % VN == 0 && ld_u % VN == 0 && pb_aligned_dev(u, 16);
+    auto act = [](float v) { return FIXED ? silu_f(v) : v; };
     if (N < NPAD) {                                                               // rows past N are read as zeros by the lanes
         if (!computes)
             for (int idx = lt; idx < 2 * BUF; idx += 128) sm[idx] = 0.f;
@@ -203,16 +212,16 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
     auto load_chunk = [&](int k) {
         float* buf = sm + (k & 1) * BUF;
         const int t0 = k * CHUNK, cnt = min(CHUNK, n_tok - t0);
-        const T* rows = u + (size_t)(first + t0) * channels;
+        const T* rows = u + (size_t)(first + t0) * ld_u;
         // everything a thread fetches for the chunk is asked for before anything is stored: one wait per chunk
         float xv[(CHUNK * SCAN_COLS + 127) / 128];
 #pragma unroll
         for (int it = 0; it < (CHUNK * SCAN_COLS + 127) / 128; ++it) {
             const int idx = lt + it * 128;
             const int tt = idx / SCAN_COLS, cc = idx % SCAN_COLS;
-            xv[it] = (idx < cnt * SCAN_COLS && p_first + cc < P) ? pb_ld(rows + (size_t)tt * channels + h * P + p_first + cc) : 0.f;
+            xv[it] = (idx < cnt * SCAN_COLS && p_first + cc < P) ? act(pb_ld(rows + (size_t)tt * ld_u + h * P + p_first + cc)) : 0.f;
         }
-        const float dt_raw = lt < cnt ? pb_ld(dt_in + (size_t)(first + t0 + lt) * ld_dt + h) : 0.f;
+        const float dt_raw = (!FIXED && lt < cnt) ? pb_ld(dt_in + (size_t)(first + t0 + lt) * ld_dt + h) : 0.f;
         if (vec) {
             // B and C of a token: 2 N / VN pieces of 16 bytes; four of a thread's loads in flight at a time
             const int per_tok = 2 * (N / VN), total = cnt * per_tok;
@@ -223,7 +232,7 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
                     const int idx = base + it * 128;
                     if (idx < total) {
                         const int tt = idx / per_tok, rem = idx - tt * per_tok;
-                        pb_ld_vec(rows + (size_t)tt * channels + inner + g * N + (rem >= N / VN ? (groups - 1) * N : 0) + rem * VN, v[it]);
+                        pb_ld_vec(rows + (size_t)tt * ld_u + inner + g * N + (rem >= N / VN ? (groups - 1) * N : 0) + rem * VN, v[it]);
                     }
                 }
 #pragma unroll
@@ -234,7 +243,8 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
                         const bool is_c = rem >= N / VN;
                         float* dst = buf + (is_c ? CHUNK * NPAD : 0) + tt * NPAD + (is_c ? rem - N / VN : rem) * VN;
 #pragma unroll
-                        for (int e = 0; e < VN; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(v[it][e], v[it][e + 1], v[it][e + 2], v[it][e + 3]);
+                        for (int e = 0; e < VN; e += 4)
+                            *reinterpret_cast<float4*>(dst + e) = make_float4(act(v[it][e]), act(v[it][e + 1]), act(v[it][e + 2]), act(v[it][e + 3]));
                     }
                 }
             }
@@ -246,9 +256,9 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
                     const int idx = base + it * 128;
                     if (idx < cnt * N) {
                         const int tt = idx / N, n = idx - tt * N;
-                        const T* row = rows + (size_t)tt * channels + inner + g * N;
-                        vb[it] = pb_ld(row + n);
-                        vc[it] = pb_ld(row + groups * N + n);
+                        const T* row = rows + (size_t)tt * ld_u + inner + g * N;
+                        vb[it] = act(pb_ld(row + n));
+                        vc[it] = act(pb_ld(row + groups * N + n));
                     }
                 }
 #pragma unroll
@@ -267,7 +277,7 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
             const int idx = lt + it * 128;
             if (idx < cnt * SCAN_COLS) buf[2 * CHUNK * NPAD + idx] = xv[it];
         }
-        if (lt < cnt) {
+        if (!FIXED && lt < cnt) {
             const float dt = softplus_f(dt_raw + bias);
             buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + lt] = dt;
             buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + CHUNK + lt] = expf(neg_a * dt);
@@ -283,8 +293,9 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
             const int t0 = k * CHUNK, cnt = min(CHUNK, n_tok - t0);
             for (int tt = 0; tt < cnt; ++tt) {
                 const float x = buf[2 * CHUNK * NPAD + tt * SCAN_COLS + colp];
-                const float dt = buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + tt], decay = buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + CHUNK + tt];
-                const float dx = dt * x;
+                const float dt = FIXED ? 1.0f : buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + tt];
+                const float decay = FIXED ? neg_a : buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + CHUNK + tt];
+                const float dx = FIXED ? x : dt * x;
                 const float4* b4 = reinterpret_cast<const float4*>(buf + tt * NPAD) + j;
                 const float4* c4 = reinterpret_cast<const float4*>(buf + CHUNK * NPAD + tt * NPAD) + j;
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;                   // four sums side by side, added up in a fixed order
@@ -300,7 +311,7 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
                 acc += __shfl_xor_sync(0xffffffffu, acc, 1);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 2);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-                if (live && j == 0) y[(size_t)(first + t0 + tt) * inner + h * P + p] = fmaf(skip, x, acc);
+                if (live && j == 0) y[(size_t)(first + t0 + tt) * inner + h * P + p] = FIXED ? acc : fmaf(skip, x, acc);
             }
         }
         __syncthreads();
@@ -315,7 +326,7 @@ ssm_scan_kernel(const T* __restrict__ u, const T* __restrict__ dt_in, long long 
 template <typename T>
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long ld_z,
                                            const float* __restrict__ w, T* __restrict__ out, int inner, int parts, float eps,
-                                           int gate_after) {
+                                           int gate_after, int sigmoid_gate) {
     pb_grid_dep_launch();
     pb_grid_dep_wait();
     __shared__ float red[32];
@@ -323,7 +334,8 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     const float* yr = y + (size_t)t * inner + (size_t)part * width;
     const T* zr = z + (size_t)t * ld_z + (size_t)part * width;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = gate_after ? yr[i] : yr[i] * silu_f(pb_ld(zr + i)); ss += v * v; }
+    auto gate = [&](float z) { return sigmoid_gate ? 1.0f / (1.0f + expf(-z)) : silu_f(z); };
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = gate_after ? yr[i] : yr[i] * gate(pb_ld(zr + i)); ss += v * v; }
     ss = pb_warp_sum(ss);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     if (lane == 0) red[warp] = ss;
@@ -333,7 +345,7 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     const float inv = 1.0f / sqrtf(total / (float)width + eps);
     T* o = out + (size_t)t * inner + (size_t)part * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x)
-        pb_st(o + i, yr[i] * silu_f(pb_ld(zr + i)) * inv * w[(size_t)part * width + i]);   // the same product either way
+        pb_st(o + i, yr[i] * gate(pb_ld(zr + i)) * inv * w[(size_t)part * width + i]);   // the same product either way
 }
 
 template <typename TI, typename TO>
@@ -403,8 +415,9 @@ PB_API int pb_ssm_scan(const void* u, const void* dt_in, long long ld_dt, int dt
     const dim3 grid(heads * col_blocks, n_seqs), block(2 * SCAN_COLS * SCAN_LANES);
     const int npl = (N + SCAN_LANES - 1) / SCAN_LANES;
 #define SCAN_LAUNCH(NPL)                                                                                                    \
-    PB_DISPATCH_DTYPE(dtype, T, (pb_launch(ssm_scan_kernel<T, NPL>, grid, block, 0, stream, (const T*)u, (const T*)dt_in, ld_dt, \
-                                           dt_bias, a_log, d_skip, state, y, cu_q, slots, heads, P, N, groups)))
+    PB_DISPATCH_DTYPE(dtype, T, (pb_launch(ssm_scan_kernel<T, NPL, false>, grid, block, 0, stream, (const T*)u,               \
+                                           (long long)(heads * P + 2 * groups * N), (const T*)dt_in, ld_dt, dt_bias, a_log, d_skip,  \
+                                           state, y, cu_q, slots, heads, P, N, groups)))
     if (npl <= 4) SCAN_LAUNCH(4);
     else if (npl <= 8) SCAN_LAUNCH(8);
     else if (npl <= 16) SCAN_LAUNCH(16);
@@ -414,10 +427,37 @@ PB_API int pb_ssm_scan(const void* u, const void* dt_in, long long ld_dt, int dt
     return 0;
 }
 
+// Linear attention with a decaying state: per head S <- decay_h S + k v^T, o = S^T q, with q, k, v the SiLU of the
+// projection's columns.  u: the projection, rows ld_u apart, laid out [v: heads * P | k: heads * N | q: heads * N];
+// decay float32 [heads]; state float32 [slots, heads, N, P]; y float32 [n_tokens, heads * P].
+PB_API int pb_decay_scan(const void* u, long long ld_u, int dtype, const float* decay, float* state, float* y, const int32_t* cu_q,
+                         const int32_t* slots, int n_seqs, int heads, int P, int N, cudaStream_t stream) {
+    PB_REQUIRE(n_seqs >= 0 && heads > 0 && P > 0 && N > 0 && ld_u >= (long long)heads * (P + 2 * N), "decay_scan: bad sizes");
+    PB_REQUIRE(N <= 32 * SCAN_LANES, "decay_scan: keys of %d elements (at most %d)", N, 32 * SCAN_LANES);
+    PB_REQUIRE(u && decay && state && y && cu_q && slots, "decay_scan: null pointer");
+    if (n_seqs == 0) return 0;
+    PB_REQUIRE(n_seqs < 65536, "decay_scan: %d sequences in one launch", n_seqs);
+    const int col_blocks = (P + SCAN_COLS - 1) / SCAN_COLS;
+    const dim3 grid(heads * col_blocks, n_seqs), block(2 * SCAN_COLS * SCAN_LANES);
+    const int npl = (N + SCAN_LANES - 1) / SCAN_LANES;
+#define SCAN_LAUNCH(NPL)                                                                                                    \
+    PB_DISPATCH_DTYPE(dtype, T, (pb_launch(ssm_scan_kernel<T, NPL, true>, grid, block, 0, stream, (const T*)u, ld_u, (const T*)nullptr, \
+                                           0ll, (const float*)nullptr, decay, (const float*)nullptr, state, y, cu_q, slots, heads, P, \
+                                           N, heads)))
+    if (npl <= 4) SCAN_LAUNCH(4);
+    else if (npl <= 8) SCAN_LAUNCH(8);
+    else if (npl <= 16) SCAN_LAUNCH(16);
+    else SCAN_LAUNCH(32);
+#undef SCAN_LAUNCH
+    PB_CHECK_LAUNCH("decay_scan");
+    return 0;
+}
+
 // y float32 [n_tokens, inner]; z: the gate columns of the input projection, row stride ld_z; w float32 [inner];
-// out [n_tokens, inner] dense.  gate_after 0: norm(y * silu(z)) * w; 1: norm(y) * w * silu(z).
+// out [n_tokens, inner] dense.  gate_after 0: norm(y * gate(z)) * w; 1: norm(y) * w * gate(z); gate is SiLU, or the
+// sigmoid with sigmoid_gate.
 PB_API int pb_gated_group_rmsnorm(const float* y, const void* z, long long ld_z, const float* w, void* out, int dtype, int n_tokens,
-                                  int inner, int parts, float eps, int gate_after, cudaStream_t stream) {
+                                  int inner, int parts, float eps, int gate_after, int sigmoid_gate, cudaStream_t stream) {
     PB_REQUIRE(n_tokens >= 0 && inner > 0 && parts > 0 && inner % parts == 0 && ld_z >= inner, "gated_group_rmsnorm: bad sizes");
     PB_REQUIRE(y && z && w && out, "gated_group_rmsnorm: null pointer");
     if (n_tokens == 0) return 0;
@@ -426,7 +466,7 @@ PB_API int pb_gated_group_rmsnorm(const float* y, const void* z, long long ld_z,
     while (threads < 256 && threads < inner / parts) threads <<= 1;
     PB_DISPATCH_DTYPE(dtype, T,
         (pb_launch(gated_group_rmsnorm_kernel<T>, dim3(n_tokens, parts), dim3(threads), 0, stream, y, (const T*)z, ld_z, w, (T*)out, inner,
-                   parts, eps, gate_after)));
+                   parts, eps, gate_after, sigmoid_gate)));
     PB_CHECK_LAUNCH("gated_group_rmsnorm");
     return 0;
 }

@@ -311,6 +311,18 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gelu_tanh_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """gelu(gate) * up, the tanh form of GELU, on a merged projection [T, 2 I] -> [T, I]."""
+    _need(gate_up, "gate_up")
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelLibraryError("gelu_tanh_mul: the merged projection has an even number of columns")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    check(_l.library().pb_gelu_tanh_mul(gate_up.data_ptr(), out.data_ptr(), dtype_code(gate_up.dtype), T, two_i // 2, _stream()),
+          "gelu_tanh_mul")
+    return out
+
+
 def gemm_ref(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
              out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """a [M, K] times w [N, K] transposed (+ bias) on the float32 units."""
@@ -491,13 +503,19 @@ def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, group_top: int, renormalize: bool):
-    """float32 router logits [T, E] -> (experts int32 [T, top], weights float32 [T, top])."""
+def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, group_top: int, renormalize: bool,
+              correction: Optional[torch.Tensor] = None):
+    """float32 router logits [T, E] -> (experts int32 [T, top], weights float32 [T, top]).  ``correction`` float32 [E]
+    joins the scores for the choice (groups and experts) only; the weights are the scores without it."""
     _need(logits, "logits", torch.float32)
     T, E = logits.shape
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+        if correction.numel() != E:
+            raise KernelLibraryError(f"moe_route: a correction of {correction.numel()} numbers for {E} experts")
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    check(_l.library().pb_moe_route(logits.data_ptr(), T, E, top, groups, keep, group_top, 1 if renormalize else 0,
+    check(_l.library().pb_moe_route(logits.data_ptr(), _ptr(correction), T, E, top, groups, keep, group_top, 1 if renormalize else 0,
                                     ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
     return ids, weights
 
@@ -784,11 +802,32 @@ def ssm_scan(u: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: to
     return out
 
 
+def decay_scan(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, batch, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Linear attention with a decaying state over the step's tokens, sequence by sequence: per head
+    S <- decay_h S + k v^T, o = S^T q with q, k, v the SiLU of the projection's columns.  proj [T, >= H (P + 2 N)] a view
+    with dense rows laid out [v: H P | k: H N | q: H N | ...], decay float32 [H], state float32 [slots, H, N, P];
+    returns o float32 [T, H P].  See csrc/ssm.cu."""
+    T = proj.shape[0]
+    _rows_view(proj, "proj", T, None)
+    _need(decay, "decay", torch.float32)
+    _need(state, "state", torch.float32)
+    _, H, N, P = state.shape
+    if proj.shape[1] < H * (P + 2 * N) or decay.numel() != H:
+        raise KernelLibraryError(f"decay_scan: proj {tuple(proj.shape)}, state {tuple(state.shape)}, {decay.numel()} decays")
+    if out is None:
+        out = torch.empty((T, H * P), dtype=torch.float32, device=proj.device)
+    check(_l.library().pb_decay_scan(proj.data_ptr(), proj.stride(0), dtype_code(proj.dtype), decay.data_ptr(), state.data_ptr(),
+                                     out.data_ptr(), batch.cu_q.data_ptr(), batch.state_slots.data_ptr(), batch.cu_q.numel() - 1, H, P, N,
+                                     _stream()), "decay_scan")
+    return out
+
+
 def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int, eps: float,
-                        out: Optional[torch.Tensor] = None, gate_after: bool = False) -> torch.Tensor:
+                        out: Optional[torch.Tensor] = None, gate_after: bool = False, sigmoid_gate: bool = False) -> torch.Tensor:
     """y * silu(z) brought to unit root mean square in ``parts`` equal parts, times weight; with ``gate_after`` y
-    brought to unit root mean square in parts, times weight, times silu(z).  y float32 [T, inner], z a view
-    [T, inner] with dense rows of the run's type, which the result has too."""
+    brought to unit root mean square in parts, times weight, times silu(z); with ``sigmoid_gate`` the gate is
+    sigmoid(z) instead of silu(z).  y float32 [T, inner], z a view [T, inner] with dense rows of the run's type,
+    which the result has too."""
     _need(y, "y", torch.float32)
     _need(z, "z", contiguous=False)
     _need(weight, "weight", torch.float32)
@@ -798,7 +837,8 @@ def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, 
     if out is None:
         out = torch.empty((T, inner), dtype=z.dtype, device=y.device)
     check(_l.library().pb_gated_group_rmsnorm(y.data_ptr(), z.data_ptr(), z.stride(0), weight.data_ptr(), out.data_ptr(),
-                                              dtype_code(z.dtype), T, inner, parts, float(eps), 1 if gate_after else 0, _stream()),
+                                              dtype_code(z.dtype), T, inner, parts, float(eps), 1 if gate_after else 0,
+                                              1 if sigmoid_gate else 0, _stream()),
           "gated_group_rmsnorm")
     return out
 
@@ -890,16 +930,24 @@ def _rows_view(t: torch.Tensor, name: str, rows: int, dtype) -> None:
 
 def heads_prepare(q_in: torch.Tensor, k_in: Optional[torch.Tensor], v_in: Optional[torch.Tensor], *, n_heads: int, q_dim: int,
                   q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
-                  rates: Optional[torch.Tensor] = None, rot_dims: int = 0, adjacent: bool = False,
+                  norm: Optional[str] = None, rates: Optional[torch.Tensor] = None, amplitude: float = 1.0, rot_dims: int = 0,
+                  adjacent: bool = False,
                   v_other: Optional[torch.Tensor] = None, v_copy: Optional[torch.Tensor] = None, mix: float = 0.0,
                   positions: torch.Tensor, table_row: torch.Tensor, block_table: Optional[torch.Tensor] = None,
                   q_out: torch.Tensor, k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
                   status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Per-head norm (one scale for all heads), rotation by rates, values blended with another layer's; queries to
+    """Per-head norm (one scale for all heads, or none: ``norm`` is None for no norm, "before" or "after" the rotation;
+    left out it is "before" where scales are given), rotation by rates with cosine and sine times ``amplitude``, values
+    blended with another layer's; queries to
     ``q_out``, keys and values into pages; see csrc/heads_prepare.cu.  ``q_in``, ``k_in``, ``v_in`` are [T, cols] views
     with dense rows; ``v_other`` / ``v_copy`` dense [T, value cols]; ``k_pages`` None: nothing is cached."""
     T, dt = q_in.shape[0], q_in.dtype
     _rows_view(q_in, "q_in", T, dt)
+    if norm is None and (q_weight is not None or k_weight is not None):
+        norm = "before"
+    if norm not in (None, "before", "after"):
+        raise KernelLibraryError(f"heads_prepare: norm is None, 'before' or 'after', not {norm!r}")
+    norm_code = {None: 0, "before": 1, "after": 2}[norm]
     for t, name in ((q_weight, "q_weight"), (k_weight, "k_weight"), (rates, "rates")):
         if t is not None:
             _need(t, name, torch.float32)
@@ -941,7 +989,8 @@ def heads_prepare(q_in: torch.Tensor, k_in: Optional[torch.Tensor], v_in: Option
         raise KernelLibraryError("heads_prepare: blended values need pages")
     check(_l.library().pb_heads_prepare(
         q_in.data_ptr(), q_in.stride(0), _ptr(k_in), 0 if k_in is None else k_in.stride(0), _ptr(v_in),
-        0 if v_in is None else v_in.stride(0), dtype_code(dt), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(rates), int(rot_dims),
+        0 if v_in is None else v_in.stride(0), dtype_code(dt), _ptr(q_weight), _ptr(k_weight), norm_code, float(eps), _ptr(rates),
+        float(amplitude), int(rot_dims),
         1 if adjacent else 0, _ptr(v_other), _ptr(v_copy), ld_other, float(mix), positions.data_ptr(), table_row.data_ptr(),
         _ptr(block_table), stride, page_size, num_pages, q_out.data_ptr(), _ptr(k_pages), _ptr(v_pages), T, n_heads, q_dim, G, kd, Gv,
         vd, _ptr(status), _stream()), "heads_prepare")

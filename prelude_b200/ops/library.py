@@ -10,7 +10,7 @@ import threading
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint64, c_void_p
 from typing import Optional
 
-ABI_VERSION = 20
+ABI_VERSION = 21
 
 
 class KernelLibraryError(RuntimeError):
@@ -72,7 +72,7 @@ _SIGNATURES = {
     "pb_diff_attention_tc_max_splits": ([I, I], I),
     "pb_diff_attention_tc_bf16": ([P, L, P, L, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, I, F, F, F, I, I, I, I, I, P, P, P], I),
     "pb_router_logits": ([P, L, P, P, I, I, I, I, P], I),
-    "pb_moe_route": ([P, I, I, I, I, I, I, I, P, P, P], I),
+    "pb_moe_route": ([P, P, I, I, I, I, I, I, I, P, P, P], I),
     "pb_moe_tile_rows": ([I, I], I),
     "pb_moe_sort": ([P, I, I, P, P, P, P, P, I, I, P], I),
     "pb_moe_gemm": ([P, L, P, I, P, L, I, I, I, P, P, P, I, I, P, L, I, I, P], I),
@@ -90,14 +90,16 @@ _SIGNATURES = {
     "pb_causal_conv_silu": ([P, L, P, P, P, P, I, P, P, P, P, I, I, I, P], I),
     "pb_conv_state_update": ([P, L, P, I, P, P, I, I, I, P], I),
     "pb_ssm_scan": ([P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P], I),
-    "pb_gated_group_rmsnorm": ([P, P, L, P, P, I, I, I, I, F, I, P], I),
+    "pb_gated_group_rmsnorm": ([P, P, L, P, P, I, I, I, I, F, I, I, P], I),
+    "pb_decay_scan": ([P, L, I, P, P, P, P, P, I, I, I, I, P], I),
+    "pb_gelu_tanh_mul": ([P, P, I, I, I, P], I),
     "pb_scaled_sum": ([P, F, P, F, P, I, I, L, P], I),
     "pb_gemm_pair_grouped_bf16": ([P, P, P, I, I, I, I, L, L, L, I, P, P, P, I, I, P, P], I),
     "pb_scaled_add_rmsnorm": ([P, I, L, F, P, P, I, I, P, P, I, I, F, P], I),
     "pb_normed_pair_sum": ([P, P, F, P, P, F, F, P, I, I, I, P], I),
     "pb_embed_gather_scaled": ([P, P, I, F, P, I, I, I, P], I),
     "pb_tanh": ([P, P, I, L, P], I),
-    "pb_heads_prepare": ([P, L, P, L, P, L, I, P, P, F, P, I, I, P, P, L, F, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, P, P], I),
+    "pb_heads_prepare": ([P, L, P, L, P, L, I, P, P, I, F, P, F, I, I, P, P, L, F, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, P, P], I),
     "pb_gated_delta_scan": ([P, L, P, L, P, L, I, P, P, P, P, P, P, I, I, I, I, I, P], I),
     "pb_token_shift_mix": ([P, P, P, P, I, P, P, P, P, I, I, I, P], I),
     "pb_wkv_scan": ([P, L, P, L, P, L, P, L, I, P, P, P, P, P, P, I, I, I, P], I),

@@ -1,5 +1,5 @@
 """Grouped-query softmax attention with the options of ``MaskedAttentionSpec``: a norm of every q and k head with one
-scale shared by the heads, rotation by rates (or none), a window that keeps the first tokens visible or a mask of
+scale shared by the heads (or none; before the rotation or after it), rotation by rates (or none), a window that keeps the first tokens visible or a mask of
 chunks, capped scores, a sink per head, a gate per head on the output, and values blended with those of the first
 layer that shares the blend's key.
 
@@ -62,7 +62,7 @@ class MaskedAttention:
                 req[f"{p}.{name}{s.bias_suffix}"] = TensorReq((n,), "bias")
         if s.o_bias:
             req[f"{p}.{s.o_name}{s.bias_suffix}"] = TensorReq((s.hidden_size,), "bias")
-        if s.head_norm_eps is not None:
+        if s.head_norm_eps is not None and s.head_norm_scale:
             req[f"{p}.{s.q_name}{s.norm_suffix}"] = TensorReq((s.head_dim,), "norm")
             req[f"{p}.{s.k_name}{s.norm_suffix}"] = TensorReq((s.head_dim,), "norm")
         if s.sink:
@@ -95,7 +95,7 @@ class MaskedAttention:
         self.w_o = mat(s.o_name).contiguous()
         if s.o_bias:
             self.b_o = vec(s.o_name + s.bias_suffix)
-        if s.head_norm_eps is not None:
+        if s.head_norm_eps is not None and s.head_norm_scale:
             self.q_norm, self.k_norm = vec(s.q_name + s.norm_suffix), vec(s.k_name + s.norm_suffix)
         if s.sink:
             self.sink = vec(s.sink_name)
@@ -126,10 +126,12 @@ class MaskedAttention:
             else:
                 v_other = shared
         rates = self.position.rates if self.rotary_dim else None
+        norm = None if s.head_norm_eps is None else ("after" if s.head_norm_after_rotation else "before")
         q = K.heads_prepare(
             proj[:, :k0], proj[:, k0:v0] if write_cache else None, proj[:, v0:g0] if write_cache else None,
             n_heads=s.num_heads, q_dim=s.head_dim, q_weight=self.q_norm, k_weight=self.k_norm, eps=s.head_norm_eps or 0.0,
-            rates=rates, rot_dims=self.rotary_dim, adjacent=bool(getattr(self.position, "adjacent", False)),
+            norm=norm, rates=rates, amplitude=float(getattr(self.position, "amplitude", 1.0)) if self.rotary_dim else 1.0,
+            rot_dims=self.rotary_dim, adjacent=bool(getattr(self.position, "adjacent", False)),
             v_other=v_other, v_copy=v_copy, mix=self.blend, positions=batch.positions, table_row=batch.table_row_of_token,
             block_table=batch.block_tables[cache.group], q_out=batch.workspace("masked_q", (T, s.num_heads, s.head_dim), x.dtype),
             k_pages=cache.k_pages if write_cache else None, v_pages=cache.v_pages if write_cache else None, status=batch.status)

@@ -18,7 +18,7 @@ from ..ops.linear import gated_linear_clamped, gated_linear_silu, linear
 from ..weights.loader import TensorReq
 from .registry import RunContext, register_part
 
-_ACTIVATIONS = {"silu": K.silu_mul}
+_ACTIVATIONS = {"silu": K.silu_mul, "gelu_tanh": K.gelu_tanh_mul}
 
 
 @register_part("feed_forward", "gated_mlp")

@@ -24,6 +24,7 @@ from . import ends as _ends  # noqa: F401
 from . import gqa as _gqa  # noqa: F401
 from . import gated_delta as _gated_delta  # noqa: F401
 from . import latent_attention as _latent_attention  # noqa: F401
+from . import linear_attention as _linear_attention  # noqa: F401
 from . import masked_attention as _masked_attention  # noqa: F401
 from . import parallel as _parallel  # noqa: F401
 from . import state_space as _state_space  # noqa: F401

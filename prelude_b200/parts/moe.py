@@ -5,7 +5,8 @@ router matrix (float32 sums of exact products on the float32 units, whatever
 the run's type: ``kernels.router_logits``).  Scores are their sigmoids; experts form equal groups of
 neighbours, a group scores the sum of its largest scores, and only experts of
 the best groups can be chosen; the chosen scores weigh the experts' outputs
-(``RoutedExpertsSpec`` has the constants).
+(``RoutedExpertsSpec`` has the constants).  A learned correction per expert may
+join the scores for the choice alone.
 
 All experts' gate and up rows live in one tensor [experts, 2 * expert_size,
 hidden] and their down rows in another [experts, hidden, expert_size].  A step
@@ -43,7 +44,7 @@ class RoutedExperts:
         if not 0 < s.top_k <= s.keep_groups * (s.n_experts // s.n_groups):
             raise ValueError(f"top_k={s.top_k} experts cannot come from {s.keep_groups} groups of {s.n_experts // s.n_groups}")
         self.spec, self.prefix = spec, prefix
-        self.w_router = self.w_gate_up = self.w_down = None
+        self.w_router = self.w_gate_up = self.w_down = self.correction = None
 
     def _expert(self, e: int, name: str) -> str:
         return f"{self.prefix}.{self.spec.expert_prefix}{e}.{name}"
@@ -51,6 +52,8 @@ class RoutedExperts:
     def tensors(self) -> Dict[str, TensorReq]:
         s = self.spec
         req = {f"{self.prefix}.{s.router_name}": TensorReq((s.n_experts, s.hidden_size))}
+        if s.correction_name is not None:
+            req[f"{self.prefix}.{s.correction_name}"] = TensorReq((s.n_experts,), "bias")
         for e in range(s.n_experts):
             req[self._expert(e, s.gate_name)] = TensorReq((s.expert_size, s.hidden_size))
             req[self._expert(e, s.up_name)] = TensorReq((s.expert_size, s.hidden_size))
@@ -64,6 +67,8 @@ class RoutedExperts:
             return get(name).to(device=ctx.device, dtype=ctx.dtype)
 
         self.w_router = mat(f"{self.prefix}.{s.router_name}").contiguous()
+        if s.correction_name is not None:
+            self.correction = get(f"{self.prefix}.{s.correction_name}").to(device=ctx.device, dtype=torch.float32).contiguous()
         self.w_gate_up = torch.stack([torch.cat([mat(self._expert(e, s.gate_name)), mat(self._expert(e, s.up_name))], dim=0)
                                       for e in range(s.n_experts)]).contiguous()
         self.w_down = torch.stack([mat(self._expert(e, s.down_name)) for e in range(s.n_experts)]).contiguous()
@@ -85,7 +90,7 @@ class RoutedExperts:
         """(experts int32 [T, top_k], weights float32 [T, top_k]) for the rows of x."""
         s = self.spec
         logits = K.router_logits(x, self.w_router)
-        return K.moe_route(logits, s.top_k, s.n_groups, s.keep_groups, s.group_score_top, s.renormalize)
+        return K.moe_route(logits, s.top_k, s.n_groups, s.keep_groups, s.group_score_top, s.renormalize, self.correction)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         s = self.spec
