@@ -212,6 +212,27 @@ def route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, r: 
     return ids, torch.gather(s, 1, ids)
 
 
+def route_margin(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, r: dict) -> torch.Tensor:
+    """[T]: by how much each token's choice is decided: the smaller of the gap between the last kept group and the
+    first one dropped, and the gap between the last chosen expert and the best allowed one not chosen.  A test in
+    reduced precision leaves out tokens whose gap is within the rounding."""
+    E, top = r["experts"], r["top"]
+    choice = torch.sigmoid(h @ w_router.T) + correction
+    margin = torch.full((h.shape[0],), math.inf, dtype=h.dtype)
+    groups = r.get("groups")
+    if groups is not None and groups["keep"] < groups["count"]:
+        per = E // groups["count"]
+        score = choice.reshape(-1, groups["count"], per).topk(min(2, per), dim=-1).values.sum(dim=-1)
+        ranked = score.sort(dim=-1, descending=True).values
+        margin = ranked[:, groups["keep"] - 1] - ranked[:, groups["keep"]]
+        allowed = torch.zeros_like(score, dtype=torch.bool).scatter_(1, score.topk(groups["keep"], dim=-1).indices, True)
+        choice = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), -math.inf)
+    ranked = choice.sort(dim=-1, descending=True).values
+    if top < E:
+        margin = torch.minimum(margin, ranked[:, top - 1] - ranked[:, top])
+    return margin
+
+
 def routed_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], mlp: dict) -> torch.Tensor:
     ids, weights = route(h, w["router"], w["correction"], mlp["router"])
     out = torch.zeros_like(h)
@@ -245,8 +266,10 @@ def feed_forward(h: torch.Tensor, w: Dict[str, torch.Tensor], mlp: dict) -> torc
     raise ValueError(f"unknown feed-forward {mlp['kind']!r}")
 
 
-def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None):
-    """Logits [T, vocab] of a whole sequence; ``layers_out`` collects the residual stream after every layer."""
+def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None,
+            margins_out: Optional[list] = None):
+    """Logits [T, vocab] of a whole sequence; ``layers_out`` collects the residual stream after every layer,
+    ``margins_out`` every router's ``route_margin``."""
     eps = cfg["norm"]["eps"]
     table = tensors["embed"].to(dtype)
     r = table[torch.as_tensor(tokens, dtype=torch.long)]
@@ -257,7 +280,10 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens, dtype=torch.flo
         a = mixer(layer["type"], r, sub(tensors, f"l{src}.mix.", dtype), layer["mixer"], eps)
         r = r + zero_centred_norm(a, tensors[f"l{src}.norm1"].to(dtype), eps)
         if layer.get("mlp") is not None:
-            f = feed_forward(r, sub(tensors, f"l{src}.mlp.", dtype), layer["mlp"])
+            fw = sub(tensors, f"l{src}.mlp.", dtype)
+            if margins_out is not None and layer["mlp"]["kind"] == "moe":
+                margins_out.append(route_margin(r, fw["router"], fw["correction"], layer["mlp"]["router"]))
+            f = feed_forward(r, fw, layer["mlp"])
             r = r + zero_centred_norm(f, tensors[f"l{src}.norm2"].to(dtype), eps)
         if layers_out is not None:
             layers_out.append(r.clone())
