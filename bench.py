@@ -26,7 +26,8 @@ requests, prompts of 128 to 2,048 tokens cut into portions of 512 beside the
 running decodes, 256 tokens each), as generated tokens a second by the wall clock.
 ``--workload pabelix`` and ``--workload kolisun`` put that design beside Qwen3 dense at equal
 layer sizes (random weights): prefill and decode steps, and the design's kernels beside their
-like, each a line of its own; ``--workload nedesun`` does so beside Kolisun and Qwen3 dense.
+like, each a line of its own; ``--workload nedesun`` and ``--workload pepolorn`` do so beside Kolisun and
+Qwen3 dense.
 None of them changes the default run or its line.
 """
 import argparse
@@ -892,6 +893,215 @@ def nedesun_compare(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --workload pepolorn: the Pepolorn design beside Kolisun (the closest design: attention beside a recurrent mixer in one
+# layer, a state-space mixer, norms on the sublayers' outputs, state slots) and Qwen3 dense at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------------
+PEPOLORN_SIZES = {
+    # width; chunked attention: heads, key/value heads, head size, chunk, rotated elements; linear attention with a decaying
+    # state: heads, key and value sizes; state-space mixer: heads, head size, state, groups; dense feed-forward width; routed
+    # experts: how many, how many per token, their width (top * expert_ff = ff: a token does the dense layer's work)
+    "2k": dict(width=2048, heads=16, kv=4, dim=128, chunk=1024, rot=64, l_heads=16, l_dim=128, l_vdim=128, ss_heads=64, ss_dim=64,
+               state=128, groups=8, ff=8192, experts=32, top=4, expert_ff=2048),
+    "4k": dict(width=4096, heads=32, kv=8, dim=128, chunk=1024, rot=64, l_heads=32, l_dim=128, l_vdim=128, ss_heads=128, ss_dim=64,
+               state=128, groups=8, ff=12288, experts=64, top=6, expert_ff=2048),
+}
+
+
+def pepolorn_config(z, layers, vocab):
+    """Layers that resemble a real model's: a state-space layer with a dense feed-forward first, then chunked attention
+    beside linear attention, then state-space layers, all with routed experts; the fifth layer runs the second's weights."""
+    par = {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": 8.0 * z["dim"] ** -0.5,
+                    "mask": {"size": z["chunk"]},
+                    "rot": {"dims": z["rot"], "base": 500000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}},
+           "right": {"heads": z["l_heads"], "dim": z["l_dim"], "vdim": z["l_vdim"],
+                     "decay": [1.0 - 2.0 ** -(3 + 6 * h / max(1, z["l_heads"] - 1)) for h in range(z["l_heads"])]},
+           "left_scale": 1.0, "right_scale": 1.0}
+    ssm = {"heads": z["ss_heads"], "vdim": z["ss_dim"], "state": z["state"], "groups": z["groups"], "conv": 4, "norm_groups": z["groups"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": 4, "keep": 2}}}
+    out = []
+    for i in range(layers):
+        layer = {"type": "parallel", "mixer": par, "mlp": moe} if i % 3 == 1 else \
+                {"type": "mamba2", "mixer": ssm, "mlp": {"kind": "dense", "ff": z["ff"]} if i == 0 else moe}
+        if i == 4:
+            layer = dict(layer, weights_of=1)
+        out.append(layer)
+    return {"architecture": "Pepolorn", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6}, "layers": out}
+
+
+def pepolorn_kernels(pk, size):
+    """The new design's kernels beside their like of the closest model, one launch each: chunked attention beside Kolisun's
+    window attention, over a prompt of 2,048 tokens and for 8 decoded tokens; the kernel between projection and attention
+    (rotation, then the norm per head) beside Kolisun's; the decaying-state scan beside the state-space scan, against the
+    bytes and operations they must do; the gate and norm behind it; the router's choice; the GELU-gated product beside the
+    SiLU-gated one."""
+    import torch
+    from prelude_b200.cache.manager import CacheManager
+    from prelude_b200.engine.batch import StepItem, build_step_batch
+    from prelude_b200.ops import kernels as K
+    from prelude_b200.ops import linear as L
+    from prelude_b200.ops.attention import paged_attention
+    from prelude_b200.ops.paged_general import attention_general
+    from prelude_b200.parts.registry import CombinedNeed, KvPagesNeed, StateNeed
+    z, kz = PEPOLORN_SIZES[size], KOLISUN_SIZES[size]
+    dev = torch.device("cuda:0")
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    out = {}
+    T, B = 2048, 8
+    H, G, D, chunk = z["heads"], z["kv"], z["dim"], z["chunk"]
+    ctx = 2 * chunk - 1                                      # the decoded token is the last of its chunk
+    LH, LN, LP = z["l_heads"], z["l_dim"], z["l_vdim"]
+    SH, P, N, SG = kz["ss_heads"], kz["ss_dim"], kz["state"], kz["groups"]
+    s_inner, s_channels = SH * P, SH * P + 2 * SG * N
+    l_cols = LH * (LP + 2 * LN)
+    needs = [KvPagesNeed(G, D, chunk=chunk), KvPagesNeed(G, D), StateNeed((LH, LN, LP), torch.float32),
+             CombinedNeed((StateNeed((SH, N, P), torch.float32), StateNeed((3, s_channels), None)))]
+    cache = CacheManager(needs, PAGE_SIZE, (B * (ctx + 16) + T) // PAGE_SIZE + 8, B + 1, dev, bf)
+    gen, plain = cache.layer_cache(0), cache.layer_cache(1)
+    for lc in (gen, plain):
+        lc.k_pages.normal_()
+        lc.v_pages.normal_()
+    scale = D ** -0.5
+    # -- one request of T prompt tokens
+    cache.add_request("p")
+    cache.grow("p", T)
+    batch = build_step_batch([StepItem("p", [0] * T, 0, [])], cache.block_tables(["p"]), [cache.slot_of("p")], dev, 10, 1 << 20)
+    cache.zero_fresh_state()
+    c_pairs = sum(i % chunk + 1 for i in range(T))
+    k_pairs = sum(min(i + 1, kz["window"]) for i in range(T))
+    q = torch.randn(T, H, D, device=dev).to(bf)
+    g0, g1 = cache.group_of[0], cache.group_of[1]
+    ms = _event_ms(lambda: attention_general(q, gen.k_pages, gen.v_pages, D, batch, g0, scale, None, None, chunk=chunk), flush=flush)
+    out["prefill_attention"] = {"chunked_ms": round(ms, 4), "chunked_tflops": round(H * c_pairs * 4 * D / ms / 1e9, 1)}
+    ms = _event_ms(lambda: paged_attention(q, plain.k_pages, plain.v_pages, batch, g1, scale, kz["window"]), flush=flush)
+    out["prefill_attention"].update(kolisun_window_ms=round(ms, 4), kolisun_window_tflops=round(H * k_pairs * 4 * D / ms / 1e9, 1))
+    # the kernel between projection and attention
+    proj = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+    rates = torch.rand(z["rot"] // 2, device=dev)
+    qo = torch.empty(T, H, D, dtype=bf, device=dev)
+    moved = T * (H + 2 * G) * D * 2 * 2
+    ms = _event_ms(lambda: K.heads_prepare(proj[:, :H * D], proj[:, H * D:(H + G) * D], proj[:, (H + G) * D:], n_heads=H, q_dim=D, eps=1e-6,
+                                           norm="after", rates=rates, amplitude=1.2, rot_dims=z["rot"], positions=batch.positions,
+                                           table_row=batch.table_row_of_token, block_table=batch.block_tables[g0], q_out=qo,
+                                           k_pages=gen.k_pages, v_pages=gen.v_pages, status=batch.status), flush=flush)
+    out["projection_to_pages"] = {"rotate_norm_us": round(ms * 1e3, 2), "rotate_norm_gbs": round(moved / ms / 1e6, 1)}
+    wq, wk = torch.ones(H * D, device=dev), torch.ones(G * D, device=dev)
+    full = torch.rand(D // 2, device=dev)
+    ms = _event_ms(lambda: K.qkv_prepare(proj[:, :H * D], proj[:, H * D:(H + G) * D], proj[:, (H + G) * D:], n_heads=H, q_dim=D, q_weight=wq,
+                                         k_weight=wk, k_norm_cols=G * D, eps=1e-6, rates=full, rot_dims=D, adjacent=True,
+                                         positions=batch.positions, table_row=batch.table_row_of_token, block_table=batch.block_tables[g1],
+                                         q_out=qo, k_pages=plain.k_pages, v_pages=plain.v_pages, swizzle_k=True, swizzle_v=True,
+                                         status=batch.status), flush=flush)
+    out["projection_to_pages"].update(kolisun_us=round(ms * 1e3, 2), kolisun_gbs=round(moved / ms / 1e6, 1))
+    # the recurrences over the prompt
+    l_state = cache.layer_cache(2).state
+    lproj = (torch.randn(T, l_cols + LH * LP, device=dev) * 0.5).to(bf)
+    decay = torch.linspace(0.9, 0.999, LH, device=dev)
+    ly = K.decay_scan(lproj, decay, l_state, batch)
+    ms_l = _event_ms(lambda: K.decay_scan(lproj, decay, l_state, batch, out=ly), flush=flush)
+    nw = torch.ones(LH * LP, device=dev)
+    ms_n = _event_ms(lambda: K.gated_group_rmsnorm(ly, lproj[:, l_cols:], nw, 1, 1e-6, gate_after=True, sigmoid_gate=True), flush=flush)
+    out["linear_attention_prefill"] = {
+        "scan_us": round(ms_l * 1e3, 2), "scan_gbs": round((T * l_cols * 2 + T * LH * LP * 4) / ms_l / 1e6, 1),
+        "scan_gflops": round(T * LH * LN * LP * 4 / ms_l / 1e6, 1), "us_per_token": round(ms_l * 1e3 / T, 3),
+        "gated_norm_us": round(ms_n * 1e3, 2), "gated_norm_gbs": round(T * LH * LP * (4 + 2 + 2) / ms_n / 1e6, 1)}
+    sc = cache.layer_cache(3)
+    s_state, s_carried = sc.children[0].state, sc.children[1].state
+    sproj = (torch.randn(T, 2 * s_inner + 2 * SG * N + SH, device=dev) * 0.5).to(bf)
+    xbc, dt = sproj[:, s_inner:s_inner + s_channels], sproj[:, s_inner + s_channels:]
+    s_conv, s_b = torch.randn(s_channels, 4, device=dev) * 0.5, torch.zeros(s_channels, device=dev)
+    shb, sal, sdd = torch.zeros(SH, device=dev), torch.zeros(SH, device=dev), torch.ones(SH, device=dev)
+    su = K.causal_conv_silu(xbc, s_conv, s_b, s_carried, batch)
+    sy = K.ssm_scan(su, dt, shb, sal, sdd, s_state, batch, SG)
+    ms_k = _event_ms(lambda: K.ssm_scan(su, dt, shb, sal, sdd, s_state, batch, SG, out=sy), flush=flush)
+    out["state_space_prefill"] = {"scan_us": round(ms_k * 1e3, 2), "scan_gbs": round((T * s_channels * 2 + T * s_inner * 4) / ms_k / 1e6, 1),
+                                  "scan_gflops": round(T * SH * N * P * 6 / ms_k / 1e6, 1), "us_per_token": round(ms_k * 1e3 / T, 3)}
+    # the router's choice, with and without the correction, and the GELU-gated product beside the SiLU-gated one
+    logits = torch.randn(T, z["experts"], device=dev)
+    corr = torch.randn(z["experts"], device=dev) * 0.3
+    ms_r = _event_ms(lambda: K.moe_route(logits, z["top"], 4, 2, 2, False, corr), flush=flush)
+    ms_p = _event_ms(lambda: K.moe_route(logits, z["top"], 4, 2, 2, False, None), flush=flush)
+    out["router_choice"] = {"corrected_us": round(ms_r * 1e3, 2), "plain_us": round(ms_p * 1e3, 2)}
+    x = (torch.randn(T, z["width"], device=dev) * 0.5).to(bf)
+    w_gu = (torch.randn(2 * z["ff"], z["width"], device=dev) * 0.02).to(bf)
+    fl = 2.0 * T * 2 * z["ff"] * z["width"]
+    ms_g = _event_ms(lambda: L.gated_linear_gelu_tanh(x, w_gu), flush=flush)
+    ms_s = _event_ms(lambda: L.gated_linear_silu(x, w_gu), flush=flush)
+    out["gated_product_prefill"] = {"gelu_us": round(ms_g * 1e3, 2), "gelu_tflops": round(fl / ms_g / 1e9, 1),
+                                    "silu_us": round(ms_s * 1e3, 2), "silu_tflops": round(fl / ms_s / 1e9, 1)}
+    cache.release("p")
+    # -- B single tokens at ctx keys
+    rids = [f"d{i}" for i in range(B)]
+    for r in rids:
+        cache.add_request(r)
+        cache.grow(r, ctx + 1)
+        cache.trim(r)
+    batch = build_step_batch([StepItem(r, [0], ctx, []) for r in rids], cache.block_tables(rids), [cache.slot_of(r) for r in rids], dev, 10, 1 << 20)
+    cache.zero_fresh_state()
+    q = torch.randn(B, H, D, device=dev).to(bf)
+    row_bytes = G * 2 * D * 2
+    ms = _event_ms(lambda: attention_general(q, gen.k_pages, gen.v_pages, D, batch, g0, scale, None, None, chunk=chunk), flush=flush, reps=20)
+    out["decode_attention"] = {"chunked_us": round(ms * 1e3, 2), "chunked_gbs": round(B * chunk * row_bytes / ms / 1e6, 1)}
+    ms = _event_ms(lambda: paged_attention(q, plain.k_pages, plain.v_pages, batch, g1, scale, kz["window"]), flush=flush, reps=20)
+    out["decode_attention"].update(kolisun_window_us=round(ms * 1e3, 2), kolisun_window_gbs=round(B * kz["window"] * row_bytes / ms / 1e6, 1))
+    ms = _event_ms(lambda: K.decay_scan(lproj[:B], decay, l_state, batch, out=ly[:B]), flush=flush, reps=20)
+    out["linear_attention_decode"] = {"scan_us": round(ms * 1e3, 2), "scan_state_gbs": round(B * LH * LN * LP * 4 * 2 / ms / 1e6, 1)}
+    ms = _event_ms(lambda: K.ssm_scan(su[:B], dt[:B], shb, sal, sdd, s_state, batch, SG, out=sy[:B]), flush=flush, reps=20)
+    out["state_space_decode"] = {"scan_us": round(ms * 1e3, 2), "scan_state_gbs": round(B * SH * N * P * 4 * 2 / ms / 1e6, 1)}
+    xs = x[:B].contiguous()
+    wb = 2 * z["ff"] * z["width"] * 2
+    ms_g = _event_ms(lambda: L.gated_linear_gelu_tanh(xs, w_gu), flush=flush, reps=20)
+    ms_s = _event_ms(lambda: L.gated_linear_silu(xs, w_gu), flush=flush, reps=20)
+    out["gated_product_decode"] = {"gelu_us": round(ms_g * 1e3, 2), "gelu_gbs": round(wb / ms_g / 1e6, 1),
+                                   "silu_us": round(ms_s * 1e3, 2), "silu_gbs": round(wb / ms_s / 1e6, 1)}
+    out["peaks"] = {"bf16_tflops": pk["bf16_tflops"], "hbm_gbs": pk["hbm_gbs"], "source": pk["source"]}
+    return out
+
+
+def pepolorn_compare(args):
+    """Prefill and decode throughput of Pepolorn beside Kolisun and Qwen3 dense at equal layer sizes (random weights,
+    bfloat16): one prompt of --prefill-tokens through the step function, and --batch requests decoding behind
+    --prefix-len tokens on the captured step, both timed on the device.  One JSON line of its own."""
+    import torch
+    pk = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    t_begin = time.time()
+    points = []
+    vocab = 32768
+    for size in args.sizes.split(","):
+        z = PEPOLORN_SIZES[size]
+        layers = args.layers or 6
+        arms = {
+            "pepolorn": pepolorn_config(z, layers, vocab),
+            "kolisun": kolisun_config(KOLISUN_SIZES[size], layers, vocab),
+            "qwen3": dict(QWEN3_4B, vocab_size=vocab, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=layers,
+                          num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["dim"], tie_word_embeddings=True),
+        }
+        point = {"size": size, "layers": layers, "width": z["width"]}
+        for name, cfg in arms.items():
+            pages_per_req = -(-(PREFIX_LEN + args.warmup + args.steps + 2) // PAGE_SIZE)
+            engine = _engine_for(cfg, args.batch * pages_per_req + 2 * (PREFILL_TOKENS // PAGE_SIZE) + 8, args.batch + 2)
+            shim = {"vocab_size": vocab}
+            prefill_ms, _ = time_prefill(engine, shim, args.warmup)
+            dec, _ = time_decode(engine, shim, args.batch, args.steps, args.warmup, seed=1)
+            point[name] = {"prefill_tok_s": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                           "decode_tok_s": round(dec["tok_s"], 1), "decode_ms_per_step": round(dec["ms_per_step"], 4),
+                           "weight_gb": round(engine.model.weight_bytes() / 1e9, 3)}
+            del engine
+            torch.cuda.empty_cache()
+        point["kernels"] = pepolorn_kernels(pk, size)
+        points.append(point)
+    clocks.stop()
+    print(json.dumps({"metric": "Pepolorn beside Kolisun and Qwen3 dense at equal layer sizes: prefill and decode tokens a second, device-timed",
+                      "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": args.steps,
+                      "warmup": args.warmup, "config": {"batch": args.batch, "prefix_len": PREFIX_LEN, "prefill_tokens": PREFILL_TOKENS,
+                                                        "page_size": PAGE_SIZE, "l2": "inputs_exceed_l2 (steps), flushed (kernels)"},
+                      "points": points, "clocks": clocks.summary([(t_begin, time.time())])}))
+    return 0
+
+
 def serve(args):
     """A mixed continuous batch through ``Engine.generate`` (host tokens in, host tokens out): ``--requests`` prompts
     of uniform random ids with lengths uniform in [128, 2048], prompts cut into portions of ``--prefill-chunk``
@@ -956,11 +1166,11 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels' timeline of one layer of the decode step to stderr (needs PRELUDE_TIMELINE=1 in the environment)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "pabelix", "kolisun", "nedesun"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "pabelix", "kolisun", "nedesun", "pepolorn"],
                     help="serving: a mixed continuous batch through Engine.generate instead of the decode step (a line of its own); "
                          "pabelix, kolisun: that design beside Qwen3 dense at equal layer sizes (a line of its own); "
-                         "nedesun: that design beside Kolisun and Qwen3 dense at equal layer sizes (a line of its own)")
-    ap.add_argument("--sizes", default="2k,4k", help="pabelix, kolisun, nedesun: which layer sizes to run (2k, 4k)")
+                         "nedesun, pepolorn: that design beside Kolisun and Qwen3 dense at equal layer sizes (a line of its own)")
+    ap.add_argument("--sizes", default="2k,4k", help="pabelix, kolisun, nedesun, pepolorn: which layer sizes to run (2k, 4k)")
     ap.add_argument("--requests", type=int, default=32, help="serving: number of requests")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="serving: tokens per portion of a prompt")
     ap.add_argument("--new-tokens", type=int, default=256, help="serving: generated tokens per request")
@@ -994,6 +1204,9 @@ def main():
     if args.workload == "nedesun":
         args.layers = 0 if args.layers == MODEL["num_hidden_layers"] else args.layers
         return nedesun_compare(args)
+    if args.workload == "pepolorn":
+        args.layers = 0 if args.layers == MODEL["num_hidden_layers"] else args.layers
+        return pepolorn_compare(args)
     import torch
     pk = peaks()
     # cache: the largest point (64 requests) with room for prefix + generated tokens, in whole pages

@@ -170,3 +170,52 @@ PB_API int pb_gelu_tanh_mul(const void* gate_up, void* out, int dtype, int n_tok
     PB_CHECK_LAUNCH("gelu_tanh_mul");
     return 0;
 }
+
+
+// SiLU in place on the first `cols` columns of rows `ld` apart, float32 arithmetic, one rounding.
+template <typename T>
+__global__ void silu_cols_kernel(T* __restrict__ x, long long ld, long long n_tokens, int cols) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tokens * cols) return;
+    T* p = x + (idx / cols) * ld + idx % cols;
+    const float v = pb_ld(p);
+    pb_st(p, v / (1.0f + expf(-v)));
+}
+
+// bfloat16, 8 elements per thread; cols % 8 == 0, ld % 8 == 0, x 16-byte aligned.
+__global__ void silu_cols_bf16x8_kernel(__nv_bfloat16* __restrict__ x, long long ld, long long n_tokens, int cols) {
+    pb_grid_dep_launch();
+    pb_grid_dep_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int per_row = cols / 8;
+    if (idx >= n_tokens * per_row) return;
+    __nv_bfloat16* p = x + (idx / per_row) * ld + (idx % per_row) * 8;
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        h[k] = __floats2bfloat162_rn(f.x / (1.0f + expf(-f.x)), f.y / (1.0f + expf(-f.y)));
+    }
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+PB_API int pb_silu_cols(void* x, long long ld, int dtype, int n_tokens, int cols, cudaStream_t stream) {
+    PB_REQUIRE(n_tokens >= 0 && cols > 0 && ld >= cols && x, "silu_cols: bad arguments");
+    if (n_tokens == 0) return 0;
+    const int threads = 256;
+    if (dtype == PB_BF16 && cols % 8 == 0 && ld % 8 == 0 && pb_aligned(x, 16)) {
+        const long long n = (long long)n_tokens * (cols / 8);
+        pb_launch(silu_cols_bf16x8_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, stream, (__nv_bfloat16*)x, ld,
+                  (long long)n_tokens, cols);
+    } else {
+        const long long n = (long long)n_tokens * cols;
+        PB_REQUIRE((n + threads - 1) / threads < (1ll << 31), "silu_cols: too many elements");
+        PB_DISPATCH_DTYPE(dtype, T, (pb_launch(silu_cols_kernel<T>, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, stream,
+                                               (T*)x, ld, (long long)n_tokens, cols)));
+    }
+    PB_CHECK_LAUNCH("silu_cols");
+    return 0;
+}

@@ -78,7 +78,7 @@ struct GpParams {
     int out_cols;
     int tiles_m, tiles_n, kblocks;
     int gated;                      // 0: plain; 1: silu(gate) * up; 2: q/k/v heads
-    int act;                        // gated 1: 0 silu(gate) * up; 1 the clamped unit a * sigmoid(alpha a) * (b + 1)
+    int act;                        // gated 1: 0 silu(gate) * up; 2 gelu(gate) * up (tanh form); 1 the clamped unit a * sigmoid(alpha a) * (b + 1)
     float limit, alpha;             //   with a = min(gate, limit), b = clamp(up, -limit, limit)
     int b_is_constant;
     // grouped form (products of routed experts over rows sorted by expert): row tile tm of the map covers the rows
@@ -413,6 +413,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         if (p.act == 1) {
                             const float a = fminf(g[j], p.limit), b = fminf(fmaxf(up[j], -p.limit), p.limit);
                             g[j] = a / (1.0f + __expf(-p.alpha * a)) * (b + 1.0f);
+                        } else if (p.act == 2) {
+                            // 0.5 z (1 + tanh(u)) = z - z / (exp(2u) + 1), u = sqrt(2 / pi) (z + 0.044715 z^3)
+                            const float z = g[j], u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+                            g[j] = (z - z / (__expf(2.0f * u) + 1.0f)) * up[j];
                         } else {
                             g[j] = g[j] / (1.0f + __expf(-g[j])) * up[j];
                         }
@@ -527,6 +531,25 @@ PB_API int pb_gemm_pair_bf16(const void* A, const void* B, const float* bias, vo
     p.out_cols = gated ? rows_b / 2 : rows_b;
     p.tiles_m = (rows_a + 255) / 256;
     p.tiles_n = gated ? (p.out_cols + GP_HALF - 1) / GP_HALF : (p.out_cols + GP_BN - 1) / GP_BN;
+    p.kblocks = (K + GP_BK - 1) / GP_BK;
+    return gp_launch(A, B, lda, ldb, p, max_pairs, stream);
+}
+
+// The gated form with the tanh form of GELU in its epilogue: out[i, j] = gelu(gate sum) * up sum; B is [2 N, K], N gate
+// rows then N up rows, a weight matrix.
+PB_API int pb_gemm_pair_gelu_glu_bf16(const void* A, const void* B, void* out, int rows_a, int rows_b, int K, long long lda,
+                                      long long ldb, long long ldo, int max_pairs, int* status, cudaStream_t stream) {
+    PB_REQUIRE(pb_gemm_pair_supported(rows_a, rows_b, K, lda, ldb, 1),
+               "gemm_pair: rows_a=%d rows_b=%d K=%d lda=%lld ldb=%lld not taken (rows must be 16-byte aligned)", rows_a, rows_b, K, lda, ldb);
+    PB_REQUIRE(A && B && out && pb_aligned(A, 16) && pb_aligned(B, 16), "gemm_pair: null or unaligned pointer");
+    if (int e = get_encode()) return e;
+    GpParams p{};
+    p.out = (__nv_bfloat16*)out; p.bias = nullptr; p.status = status; p.ldo = ldo;
+    p.rows_a = rows_a; p.rows_b = rows_b; p.K = K; p.gated = 1; p.b_is_constant = 1;
+    p.act = 2;
+    p.out_cols = rows_b / 2;
+    p.tiles_m = (rows_a + 255) / 256;
+    p.tiles_n = (p.out_cols + GP_HALF - 1) / GP_HALF;
     p.kblocks = (K + GP_BK - 1) / GP_BK;
     return gp_launch(A, B, lda, ldb, p, max_pairs, stream);
 }

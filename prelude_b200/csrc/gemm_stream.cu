@@ -68,7 +68,8 @@ struct GsParams {
     int out_f32;
     long long split_stride; // elements between the partial outputs of the splits of K (gridDim.y of them)
     int gated;              // W holds N gate rows, then N up rows; the output is silu(gate) * up, N wide
-    int act;                // gated: 0 silu(gate) * up; 1 a * sigmoid(alpha a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit)
+    int act;                // gated: 0 silu(gate) * up; 1 a * sigmoid(alpha a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit);
+                            // 2 gelu(gate) * up, the tanh form of GELU
     float limit, alpha;
     int* status;
 };
@@ -278,6 +279,8 @@ __global__ void __launch_bounds__(GS_THREADS, 1) gemm_stream_kernel(GsParams p) 
                     if (p.act == 1) {
                         const float a = fminf(gsum, p.limit), b = fminf(fmaxf(usum, -p.limit), p.limit);
                         v = a / (1.0f + expf(-p.alpha * a)) * (b + 1.0f);
+                    } else if (p.act == 2) {
+                        v = pb_gelu_tanh(gsum) * usum;
                     } else {
                         v = gsum / (1.0f + expf(-gsum)) * usum;
                     }
@@ -391,6 +394,13 @@ PB_API int pb_gemm_stream_bf16(const void* X, const void* W, const float* bias, 
                                long long ldx, long long ldw, long long ldo, int out_f32, int splits, long long split_stride,
                                int gated, int* status, cudaStream_t stream) {
     return gs_run(X, W, bias, out, M, N, K, ldx, ldw, ldo, out_f32, splits, split_stride, gated, 0, 0.f, 0.f, status, stream);
+}
+
+// The gated form with the tanh form of GELU in its epilogue: out [M, N] = gelu(x Wg^T) * (x Wu^T); W is [2 N, K], N gate
+// rows then N up rows.
+PB_API int pb_gemm_stream_gelu_glu_bf16(const void* X, const void* W, void* out, int M, int N, int K, long long ldx, long long ldw,
+                                        long long ldo, int out_f32, int* status, cudaStream_t stream) {
+    return gs_run(X, W, nullptr, out, M, N, K, ldx, ldw, ldo, out_f32, 1, 0, 1, 2, 0.f, 0.f, status, stream);
 }
 
 // The gated form with the clamped unit in its epilogue: out [M, N] = a * sigmoid(alpha a) * (b + 1) with

@@ -133,8 +133,12 @@ PB_API int pb_heads_prepare(const void* q_in, long long ldq, const void* k_in, l
                    "heads_prepare: blended values need value pages and rows of %d", Gv * vd);
     }
     if (n_tokens == 0) return 0;
+    // a warp per head at a time; a step of few tokens has few blocks, so each gets as many warps as the token has query
+    // heads (they are the most), 4 to 16
+    int threads = n_tokens < 128 ? 32 * H : 128;
+    threads = threads < 128 ? 128 : (threads > 512 ? 512 : threads);
     PB_DISPATCH_DTYPE(dtype, T,
-        (pb_launch(heads_prepare_kernel<T>, dim3(n_tokens), dim3(128), rates ? (size_t)rot_dims * sizeof(float) : 0, stream, (const T*)q_in, ldq,
+        (pb_launch(heads_prepare_kernel<T>, dim3(n_tokens), dim3(threads), rates ? (size_t)rot_dims * sizeof(float) : 0, stream, (const T*)q_in, ldq,
                    (const T*)k_in, ldk, (const T*)v_in, ldv, q_w, k_w, norm, eps, rates, amplitude, rot_dims, adjacent, (const T*)v_other, (T*)v_copy, ld_other, mix,
                    positions, table_row, block_table, table_stride, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, H, qd, G, kd, Gv,
                    vd, status)));

@@ -87,6 +87,7 @@ __device__ __forceinline__ void moe_warp_argmax(float& val, int& idx) {
     }
 }
 
+template <int SLOTS>                                         // experts per lane: n_experts <= 32 * SLOTS
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
                                                         int n_tokens, int n_experts, int top, int groups, int keep, int gtop,
                                                         int renorm, int32_t* __restrict__ ids, float* __restrict__ weights) {
@@ -97,11 +98,11 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     if (t >= n_tokens) return;
     const float* z = logits + (size_t)t * n_experts;
     const int per = n_experts / groups;
-    const int slots = (n_experts + 31) / 32;                 // experts per lane, 32 at most
+    constexpr int slots = SLOTS;
     const float NONE = -INFINITY;                            // below every choice score, negative ones included
-    float sc[32];                                            // what the choice goes by
+    float sc[SLOTS];                                         // what the choice goes by
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
+    for (int i = 0; i < SLOTS; ++i) {
         const int e = lane + 32 * i;
         sc[i] = (i < slots && e < n_experts) ? 1.0f / (1.0f + expf(-z[e])) + (correction ? correction[e] : 0.f) : NONE;
     }
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
                 float val = NONE;
                 int idx = 0x7fffffff;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < SLOTS; ++i) {
                     const int e = lane + 32 * i;
                     if (i < slots && e < n_experts && e / per == g && !((taken >> i) & 1u) && sc[i] > val) { val = sc[i]; idx = e; }
                 }
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
         float val = NONE;
         int idx = 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < SLOTS; ++i) {
             const int e = lane + 32 * i;
             if (i < slots && e < n_experts && ((allowed >> (e / per)) & 1ull) && !((chosen >> i) & 1u) && sc[i] > val) { val = sc[i]; idx = e; }
         }
@@ -174,8 +175,16 @@ PB_API int pb_moe_route(const float* logits, const float* correction, int n_toke
     PB_REQUIRE(top <= keep * (n_experts / groups), "moe_route: top=%d experts cannot come from %d groups of %d", top, keep, n_experts / groups);
     PB_REQUIRE(logits && ids && weights, "moe_route: null pointer");
     if (n_tokens == 0) return 0;
-    pb_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, correction, n_tokens, n_experts, top, groups,
-              keep, gtop, renorm, ids, weights);
+    const int per_lane = (n_experts + 31) / 32;
+#define ROUTE_LAUNCH(S)                                                                                                          \
+    pb_launch(moe_route_kernel<S>, dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits, correction, n_tokens, n_experts, top, groups, \
+              keep, gtop, renorm, ids, weights)
+    if (per_lane <= 1) ROUTE_LAUNCH(1);
+    else if (per_lane <= 2) ROUTE_LAUNCH(2);
+    else if (per_lane <= 4) ROUTE_LAUNCH(4);
+    else if (per_lane <= 8) ROUTE_LAUNCH(8);
+    else ROUTE_LAUNCH(32);
+#undef ROUTE_LAUNCH
     PB_CHECK_LAUNCH("moe_route");
     return 0;
 }

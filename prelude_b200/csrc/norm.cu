@@ -368,15 +368,15 @@ __global__ void normed_add_rmsnorm_kernel(const TX* __restrict__ x, const float*
     }
 }
 
-// The same for every row of the stream, four elements per thread and access, all loads of the row issued before the
-// first sum and the row kept in registers between the passes.  width % 4 == 0, width <= 4 * blockDim * ITERS.
+// The same, four elements per thread and access, all loads of the row issued before the first sum and the row kept in
+// registers between the passes; for every row of the stream, or (with `rows`) for the chosen rows, whose sum is not
+// stored.  width % 4 == 0, width <= 4 * blockDim * ITERS.
 template <typename TX, typename TY, int ITERS>
 __global__ void normed_add_rmsnorm_vec4_kernel(const TX* __restrict__ x, const float* __restrict__ wx, float eps_x,
-                                               float* __restrict__ res, const float* __restrict__ w, TY* __restrict__ y, int width,
-                                               float eps) {
+                                               float* __restrict__ res, const int32_t* __restrict__ rows, int n_rows_total,
+                                               const float* __restrict__ w, TY* __restrict__ y, int width, float eps) {
     pb_grid_dep_launch();
     __shared__ float red[32];
-    const size_t row = blockIdx.x;
     const int n4 = width >> 2;
     float4 gx[ITERS], gw[ITERS];
 #pragma unroll
@@ -388,6 +388,12 @@ __global__ void normed_add_rmsnorm_vec4_kernel(const TX* __restrict__ x, const f
         }
     }
     pb_grid_dep_wait();
+    size_t row = blockIdx.x;
+    if (rows != nullptr) {
+        const int r = rows[blockIdx.x];
+        if (r < 0 || r >= n_rows_total) return;
+        row = (size_t)r;
+    }
     float4 xv[ITERS], rv[ITERS];
     float ss = 0.f;
 #pragma unroll
@@ -420,7 +426,7 @@ __global__ void normed_add_rmsnorm_vec4_kernel(const TX* __restrict__ x, const f
             float4 v = rv[it];
             v.x += xv[it].x * inv_x * gx[it].x; v.y += xv[it].y * inv_x * gx[it].y;
             v.z += xv[it].z * inv_x * gx[it].z; v.w += xv[it].w * inv_x * gx[it].w;
-            reinterpret_cast<float4*>(res + row * width)[i] = v;
+            if (rows == nullptr) reinterpret_cast<float4*>(res + row * width)[i] = v;
             rv[it] = v;
             ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
         }
@@ -434,7 +440,7 @@ __global__ void normed_add_rmsnorm_vec4_kernel(const TX* __restrict__ x, const f
             const float4 v = rv[it], g = w ? gw[it] : make_float4(1.f, 1.f, 1.f, 1.f);
             const float o0 = w ? v.x * inv * g.x : v.x, o1 = w ? v.y * inv * g.y : v.y, o2 = w ? v.z * inv * g.z : v.z,
                         o3 = w ? v.w * inv * g.w : v.w;
-            TY* out = y + row * width + 4 * (size_t)i;
+            TY* out = y + (size_t)blockIdx.x * width + 4 * (size_t)i;       // chosen rows are stored one below the other
             if constexpr (sizeof(TY) == 2) {
                 const __nv_bfloat162 p0 = __floats2bfloat162_rn(o0, o1), p1 = __floats2bfloat162_rn(o2, o3);
                 uint2 raw;
@@ -459,12 +465,12 @@ PB_API int pb_normed_add_rmsnorm(const void* x, const float* wx, float eps_x, fl
     if (n_out == 0) return 0;
     const int threads = norm_threads(width);
     const size_t esz = dtype == PB_BF16 ? 2 : 4;
-    if (rows == nullptr && width % 4 == 0 && width <= 4 * threads * 8 && pb_aligned(x, 4 * esz) && pb_aligned(wx, 16) && pb_aligned(res, 16) &&
+    if (width % 4 == 0 && width <= 4 * threads * 8 && pb_aligned(x, 4 * esz) && pb_aligned(wx, 16) && pb_aligned(res, 16) &&
         (w == nullptr || pb_aligned(w, 16)) && (y == nullptr || pb_aligned(y, 4 * esz))) {
         const int iters = (width / 4 + threads - 1) / threads;
 #define NA_VEC(IT)                                                                                                              \
     PB_DISPATCH_DTYPE(dtype, T, (pb_launch(normed_add_rmsnorm_vec4_kernel<T, T, IT>, dim3(n_out), dim3(threads), 0, stream, (const T*)x, wx, \
-                                           eps_x, res, w, (T*)y, width, eps)))
+                                           eps_x, res, rows, n_rows_total, w, (T*)y, width, eps)))
         if (iters <= 2) NA_VEC(2);
         else if (iters <= 4) NA_VEC(4);
         else NA_VEC(8);

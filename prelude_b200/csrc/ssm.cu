@@ -75,13 +75,13 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, long long ld_i
 // The same, 16 bytes of channels per thread and a run of consecutive tokens per block (channels, row stride and
 // pointers in multiples of 16 bytes; TAPS known at compile time).  A thread keeps its channels' taps and the last
 // TAPS - 1 inputs in registers: while the run stays inside one sequence every input is read once.
-#define CONV_RUN 16
+#define CONV_RUN 16                                          // a long step; a step of few tokens gives every token a block
 template <typename T, int TAPS>
 __global__ void causal_conv_silu_vec_kernel(const T* __restrict__ in, long long ld_in, const float* __restrict__ w,
                                             const float* __restrict__ bias, const T* __restrict__ carried, T* __restrict__ out,
                                             const int32_t* __restrict__ token_seq, const int32_t* __restrict__ positions,
                                             const int32_t* __restrict__ q_start, const int32_t* __restrict__ slots, int n_tokens,
-                                            int channels) {
+                                            int channels, int run) {
     constexpr int VN = 16 / sizeof(T);
     pb_grid_dep_launch();
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VN;
@@ -96,8 +96,8 @@ __global__ void causal_conv_silu_vec_kernel(const T* __restrict__ in, long long 
     pb_grid_dep_wait();
     float win[TAPS][VN];                                   // win[j]: the input under tap j
     int prev_seq = -1;
-    const int t_end = min(n_tokens, (int)(blockIdx.x + 1) * CONV_RUN);
-    for (int t = blockIdx.x * CONV_RUN; t < t_end; ++t) {
+    const int t_end = min(n_tokens, (int)(blockIdx.x + 1) * run);
+    for (int t = blockIdx.x * run; t < t_end; ++t) {
         const int seq = token_seq[t];
         if (seq < 0) { prev_seq = -1; continue; }          // a padding row
         const int i = positions[t] - q_start[seq];
@@ -157,18 +157,21 @@ __global__ void conv_state_update_kernel(const T* __restrict__ in, long long ld_
 // y[p] = sum_n S[n][p] C[n] (own rows in ascending order, then the 8 lanes by three exchanges) + D x[p].
 #define SCAN_COLS 16
 #define SCAN_LANES 8
+#ifndef SCAN_UNROLL
+#define SCAN_UNROLL 4
+#endif
 
 //
 // FIXED: the same recurrence with a decay per head that is a constant of the model and no step size (linear attention
 // with a decaying state: S <- decay_h S + k v^T, o = S^T q).  x, B, C are then v, k, q read straight from the
 // projection's columns (rows `ld_u` apart) and passed through SiLU by the loaders, in float32; dt is 1, D is 0, and
-// `a_log` holds the decays themselves.
+// `a_log` holds the decays themselves.  With `activate` 0 the columns hold SiLU's values already.
 template <typename T, int NPL, bool FIXED>
 __global__ void __launch_bounds__(256)
 ssm_scan_kernel(const T* __restrict__ u, long long ld_u, const T* __restrict__ dt_in, long long ld_dt, const float* __restrict__ dt_bias,
                 const float* __restrict__ a_log, const float* __restrict__ d_skip, float* __restrict__ state,
                 float* __restrict__ y, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ slots, int heads, int P,
-                int N, int groups) {
+                int N, int groups, int activate) {
     constexpr int NPAD = NPL * SCAN_LANES;                     // state rows with padding: a power of two
     constexpr int CHUNK = NPL == 32 ? 8 : 16;                  // tokens per chunk
     constexpr int BUF = CHUNK * (2 * NPAD + SCAN_COLS + 2);    // floats per half: B, C, x, dt, decay
@@ -203,7 +206,9 @@ ssm_scan_kernel(const T* __restrict__ u, long long ld_u, const T* __restrict__ d
     const int lt = tid - SCAN_COLS * SCAN_LANES;
     constexpr int VN = 16 / sizeof(T);                                            // elements of a 16-byte load
     const bool vec = N % VN == 0 && channels % VN == 0 && inner % VN == 0 && ld_u % VN == 0 && pb_aligned_dev(u, 16);
-    auto act = [](float v) { return FIXED ? silu_f(v) : v; };
+    // every block of a head's columns activates the head's keys and queries anew; a long step has them activated once,
+    // in place, by a kernel ahead of this one (`activate` 0)
+    auto act = [activate](float v) { return (FIXED && activate) ? silu_f(v) : v; };
     if (N < NPAD) {                                                               // rows past N are read as zeros by the lanes
         if (!computes)
             for (int idx = lt; idx < 2 * BUF; idx += 128) sm[idx] = 0.f;
@@ -291,7 +296,7 @@ ssm_scan_kernel(const T* __restrict__ u, long long ld_u, const T* __restrict__ d
         } else {
             const float* buf = sm + (k & 1) * BUF;
             const int t0 = k * CHUNK, cnt = min(CHUNK, n_tok - t0);
-            for (int tt = 0; tt < cnt; ++tt) {
+            auto token = [&](int tt) {
                 const float x = buf[2 * CHUNK * NPAD + tt * SCAN_COLS + colp];
                 const float dt = FIXED ? 1.0f : buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + tt];
                 const float decay = FIXED ? neg_a : buf[2 * CHUNK * NPAD + CHUNK * SCAN_COLS + CHUNK + tt];
@@ -312,6 +317,15 @@ ssm_scan_kernel(const T* __restrict__ u, long long ld_u, const T* __restrict__ d
                 acc += __shfl_xor_sync(0xffffffffu, acc, 2);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 4);
                 if (live && j == 0) y[(size_t)(first + t0 + tt) * inner + h * P + p] = FIXED ? acc : fmaf(skip, x, acc);
+            };
+            // a whole chunk is unrolled so that a token's loads from shared memory are under way while the token before
+            // it is still being summed over its lanes; the arithmetic and its order are the same either way
+            constexpr int UNROLL = SCAN_UNROLL;
+            if (cnt == CHUNK) {
+#pragma unroll UNROLL
+                for (int tt = 0; tt < CHUNK; ++tt) token(tt);
+            } else {
+                for (int tt = 0; tt < cnt; ++tt) token(tt);
             }
         }
         __syncthreads();
@@ -369,10 +383,11 @@ PB_API int pb_causal_conv_silu(const void* in, long long ld_in, const float* w, 
     PB_REQUIRE((channels + 127) / 128 < 65536, "causal_conv_silu: %d channels in one launch", channels);
     const int vn = dtype == PB_BF16 ? 8 : 4;
     if (taps >= 2 && taps <= 4 && channels % vn == 0 && ld_in % vn == 0 && pb_aligned(in, 16) && pb_aligned(out, 16) && pb_aligned(carried, 16)) {
-        const dim3 grid((n_tokens + CONV_RUN - 1) / CONV_RUN, (channels / vn + 63) / 64);
+        const int run = n_tokens <= 64 ? 1 : CONV_RUN;
+        const dim3 grid((n_tokens + run - 1) / run, (channels / vn + 63) / 64);
 #define CONV_LAUNCH(TAPS)                                                                                                     \
     PB_DISPATCH_DTYPE(dtype, T, (pb_launch(causal_conv_silu_vec_kernel<T, TAPS>, grid, dim3(64), 0, stream, (const T*)in, ld_in, w, bias, \
-                                           (const T*)carried, (T*)out, token_seq, positions, q_start, slots, n_tokens, channels)))
+                                           (const T*)carried, (T*)out, token_seq, positions, q_start, slots, n_tokens, channels, run)))
         if (taps == 2) CONV_LAUNCH(2);
         else if (taps == 3) CONV_LAUNCH(3);
         else CONV_LAUNCH(4);
@@ -417,7 +432,7 @@ PB_API int pb_ssm_scan(const void* u, const void* dt_in, long long ld_dt, int dt
 #define SCAN_LAUNCH(NPL)                                                                                                    \
     PB_DISPATCH_DTYPE(dtype, T, (pb_launch(ssm_scan_kernel<T, NPL, false>, grid, block, 0, stream, (const T*)u,               \
                                            (long long)(heads * P + 2 * groups * N), (const T*)dt_in, ld_dt, dt_bias, a_log, d_skip,  \
-                                           state, y, cu_q, slots, heads, P, N, groups)))
+                                           state, y, cu_q, slots, heads, P, N, groups, 0)))
     if (npl <= 4) SCAN_LAUNCH(4);
     else if (npl <= 8) SCAN_LAUNCH(8);
     else if (npl <= 16) SCAN_LAUNCH(16);
@@ -429,9 +444,10 @@ PB_API int pb_ssm_scan(const void* u, const void* dt_in, long long ld_dt, int dt
 
 // Linear attention with a decaying state: per head S <- decay_h S + k v^T, o = S^T q, with q, k, v the SiLU of the
 // projection's columns.  u: the projection, rows ld_u apart, laid out [v: heads * P | k: heads * N | q: heads * N];
-// decay float32 [heads]; state float32 [slots, heads, N, P]; y float32 [n_tokens, heads * P].
+// decay float32 [heads]; state float32 [slots, heads, N, P]; y float32 [n_tokens, heads * P].  activated: the columns
+// hold silu(v), silu(k), silu(q) already (pb_silu_cols), the scan takes them as they are.
 PB_API int pb_decay_scan(const void* u, long long ld_u, int dtype, const float* decay, float* state, float* y, const int32_t* cu_q,
-                         const int32_t* slots, int n_seqs, int heads, int P, int N, cudaStream_t stream) {
+                         const int32_t* slots, int n_seqs, int heads, int P, int N, int activated, cudaStream_t stream) {
     PB_REQUIRE(n_seqs >= 0 && heads > 0 && P > 0 && N > 0 && ld_u >= (long long)heads * (P + 2 * N), "decay_scan: bad sizes");
     PB_REQUIRE(N <= 32 * SCAN_LANES, "decay_scan: keys of %d elements (at most %d)", N, 32 * SCAN_LANES);
     PB_REQUIRE(u && decay && state && y && cu_q && slots, "decay_scan: null pointer");
@@ -443,7 +459,7 @@ PB_API int pb_decay_scan(const void* u, long long ld_u, int dtype, const float* 
 #define SCAN_LAUNCH(NPL)                                                                                                    \
     PB_DISPATCH_DTYPE(dtype, T, (pb_launch(ssm_scan_kernel<T, NPL, true>, grid, block, 0, stream, (const T*)u, ld_u, (const T*)nullptr, \
                                            0ll, (const float*)nullptr, decay, (const float*)nullptr, state, y, cu_q, slots, heads, P, \
-                                           N, heads)))
+                                           N, heads, activated ? 0 : 1)))
     if (npl <= 4) SCAN_LAUNCH(4);
     else if (npl <= 8) SCAN_LAUNCH(8);
     else if (npl <= 16) SCAN_LAUNCH(16);

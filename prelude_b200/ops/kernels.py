@@ -802,11 +802,17 @@ def ssm_scan(u: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: to
     return out
 
 
+# tokens of a step from which the linear attention's inputs are activated once, in place, ahead of the scan: every block
+# of a head's columns would otherwise activate the head's keys and queries anew
+DECAY_SCAN_ACTIVATE_AHEAD = 64
+
+
 def decay_scan(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, batch, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Linear attention with a decaying state over the step's tokens, sequence by sequence: per head
     S <- decay_h S + k v^T, o = S^T q with q, k, v the SiLU of the projection's columns.  proj [T, >= H (P + 2 N)] a view
     with dense rows laid out [v: H P | k: H N | q: H N | ...], decay float32 [H], state float32 [slots, H, N, P];
-    returns o float32 [T, H P].  See csrc/ssm.cu."""
+    returns o float32 [T, H P].  A step of many tokens has the SiLU taken in place first (``proj`` then holds the
+    activated values); a step of few leaves it to the scan's loaders.  See csrc/ssm.cu."""
     T = proj.shape[0]
     _rows_view(proj, "proj", T, None)
     _need(decay, "decay", torch.float32)
@@ -816,9 +822,12 @@ def decay_scan(proj: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, bat
         raise KernelLibraryError(f"decay_scan: proj {tuple(proj.shape)}, state {tuple(state.shape)}, {decay.numel()} decays")
     if out is None:
         out = torch.empty((T, H * P), dtype=torch.float32, device=proj.device)
+    ahead = T >= DECAY_SCAN_ACTIVATE_AHEAD
+    if ahead:
+        check(_l.library().pb_silu_cols(proj.data_ptr(), proj.stride(0), dtype_code(proj.dtype), T, H * (P + 2 * N), _stream()), "silu_cols")
     check(_l.library().pb_decay_scan(proj.data_ptr(), proj.stride(0), dtype_code(proj.dtype), decay.data_ptr(), state.data_ptr(),
                                      out.data_ptr(), batch.cu_q.data_ptr(), batch.state_slots.data_ptr(), batch.cu_q.numel() - 1, H, P, N,
-                                     _stream()), "decay_scan")
+                                     1 if ahead else 0, _stream()), "decay_scan")
     return out
 
 

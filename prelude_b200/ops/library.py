@@ -62,6 +62,8 @@ _SIGNATURES = {
     "pb_decode_advance": ([P, P, P, P, P, I, I, P], I),
     "pb_gemm_stream_clamped_glu_bf16": ([P, P, P, I, I, I, L, L, L, I, F, F, P, P], I),
     "pb_gemm_pair_clamped_glu_bf16": ([P, P, P, I, I, I, L, L, L, F, F, I, P, P], I),
+    "pb_gemm_stream_gelu_glu_bf16": ([P, P, P, I, I, I, L, L, L, I, P, P], I),
+    "pb_gemm_pair_gelu_glu_bf16": ([P, P, P, I, I, I, L, L, L, I, P, P], I),
     "pb_embed_sinusoid": ([P, P, P, I, P, P, I, I, I, P], I),
     "pb_clamped_glu": ([P, P, I, I, I, F, F, P], I),
     "pb_normed_add_rmsnorm": ([P, P, F, P, P, I, I, P, P, I, I, F, P], I),
@@ -91,7 +93,8 @@ _SIGNATURES = {
     "pb_conv_state_update": ([P, L, P, I, P, P, I, I, I, P], I),
     "pb_ssm_scan": ([P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P], I),
     "pb_gated_group_rmsnorm": ([P, P, L, P, P, I, I, I, I, F, I, I, P], I),
-    "pb_decay_scan": ([P, L, I, P, P, P, P, P, I, I, I, I, P], I),
+    "pb_decay_scan": ([P, L, I, P, P, P, P, P, I, I, I, I, I, P], I),
+    "pb_silu_cols": ([P, L, I, I, I, P], I),
     "pb_gelu_tanh_mul": ([P, P, I, I, I, P], I),
     "pb_scaled_sum": ([P, F, P, F, P, I, I, L, P], I),
     "pb_gemm_pair_grouped_bf16": ([P, P, P, I, I, I, I, L, L, L, I, P, P, P, I, I, P, P], I),

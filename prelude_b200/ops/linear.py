@@ -114,6 +114,31 @@ def gated_linear_clamped(x: torch.Tensor, weight_gate_up: torch.Tensor, limit: f
     return None
 
 
+def gated_linear_gelu_tanh(x: torch.Tensor, weight_gate_up: torch.Tensor) -> Optional[torch.Tensor]:
+    """gelu(x Wg^T) * (x Wu^T), the tanh form of GELU, for the merged [gate; up] weight in one kernel, as
+    ``gated_linear_silu``: the streaming kernel for a decode step, the paired-block kernel for the many rows of a prompt
+    step; None otherwise."""
+    if x.dtype != torch.bfloat16 or weight_gate_up.dtype != torch.bfloat16 or weight_gate_up.shape[0] % 2:
+        return None
+    M, Kdim = x.shape
+    N = weight_gate_up.shape[0] // 2
+    if stream_takes(x, weight_gate_up):
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        check(_l.library().pb_gemm_stream_gelu_glu_bf16(
+            x.data_ptr(), weight_gate_up.data_ptr(), out.data_ptr(), M, N, Kdim, x.stride(0), weight_gate_up.stride(0), N, 0,
+            tc_status(x.device).data_ptr(), _l.current_stream_ptr(x.device)), "gemm_stream (GELU-gated)")
+        return out
+    # (operands no smaller than one copy box of the kernel: 128 rows of 64 elements)
+    if (PREFILL_GEMM != "cublas" and M >= PAIR_MIN_ROWS and N >= 128 and Kdim >= 64 and pair_takes(x, weight_gate_up, gated=True)):
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        check(_l.library().pb_gemm_pair_gelu_glu_bf16(
+            x.data_ptr(), weight_gate_up.data_ptr(), out.data_ptr(), M, weight_gate_up.shape[0], Kdim, x.stride(0),
+            weight_gate_up.stride(0), out.stride(0), 0, tc_status(x.device).data_ptr(), _l.current_stream_ptr(x.device)),
+            "gemm_pair (GELU-gated)")
+        return out
+    return None
+
+
 def pair_takes(x: torch.Tensor, weight: torch.Tensor, gated: bool = False) -> bool:
     """Whether the paired-block tcgen05 kernel takes x [M, K] against weight [N, K]."""
     return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.stride(1) == 1 and weight.stride(1) == 1

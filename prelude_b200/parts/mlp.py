@@ -14,11 +14,13 @@ import torch
 
 from ..config.spec import ClampedGluSpec, GatedMlpSpec
 from ..ops import kernels as K
-from ..ops.linear import gated_linear_clamped, gated_linear_silu, linear
+from ..ops.linear import gated_linear_clamped, gated_linear_gelu_tanh, gated_linear_silu, linear
 from ..weights.loader import TensorReq
 from .registry import RunContext, register_part
 
 _ACTIVATIONS = {"silu": K.silu_mul, "gelu_tanh": K.gelu_tanh_mul}
+# the same with the activation in the epilogue of the gate/up product, where a kernel of this library takes the shape
+_FUSED = {"silu": gated_linear_silu, "gelu_tanh": gated_linear_gelu_tanh}
 
 
 @register_part("feed_forward", "gated_mlp")
@@ -53,7 +55,7 @@ class GatedMlp:
     def forward(self, x: torch.Tensor):
         """The feed-forward of x; what comes back goes to a fused residual add, which also takes
         the partial sums of a product whose K was cut into parts."""
-        act = gated_linear_silu(x, self.w_gate_up) if self.spec.activation == "silu" else None
+        act = _FUSED[self.spec.activation](x, self.w_gate_up)
         if act is None:
             act = _ACTIVATIONS[self.spec.activation](linear(x, self.w_gate_up))
         return linear(act, self.w_down, partial_sums_ok=True)
