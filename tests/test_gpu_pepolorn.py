@@ -265,6 +265,20 @@ def test_router_chooses_by_corrected_scores_and_weighs_by_plain_ones(experts, to
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("T,experts,width,pad", [(1, 6, 44, 0), (9, 32, 2048, 0), (300, 5, 128, 8), (17, 64, 200, 0), (8, 12, 100, 4), (40, 3, 7, 0)])
+def test_router_logits_are_32_bit_sums_of_exact_products(dtype, T, experts, width, pad):
+    """The router's logits against 64-bit sums, at widths the 16-byte loads take and at widths they do not, from a view
+    whose rows are further apart than they are long."""
+    from prelude_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(T + experts)
+    x = torch.randn(T, width + pad, generator=g).to(dtype)
+    w = torch.randn(experts, width, generator=g).to(dtype)
+    got = K.router_logits(x.to(DEV)[:, :width], w.to(DEV)).cpu().double()
+    want = x[:, :width].double() @ w.double().T
+    assert got.shape == want.shape and float((got - want).abs().max()) < 2e-6 * max(1.0, float(want.abs().max())) * math.sqrt(width)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("experts,top,ff,groups,T", [(6, 2, 10, (3, 2), 37), (5, 3, 14, None, 1), (8, 4, 64, (4, 2), 300), (2, 1, 16, (2, 1), 9),
                                                       (16, 2, 32, (2, 1), 70)])
 def test_routed_feed_forward_equals_the_plain_one(dtype, experts, top, ff, groups, T):
