@@ -59,7 +59,8 @@ template <typename T>
 __global__ void heads_prepare_kernel(const T* __restrict__ q_in, long long ldq, const T* __restrict__ k_in, long long ldk,
                                      const T* __restrict__ v_in, long long ldv, const float* __restrict__ q_w,
                                      const float* __restrict__ k_w, int norm, float eps, const float* __restrict__ rates,
-                                     float amplitude, int rot_dims, int adjacent, const T* __restrict__ v_other, T* __restrict__ v_copy, long long ld_other, float mix,
+                                     float amplitude, int rot_dims, int adjacent, const T* __restrict__ v_other, T* __restrict__ v_copy,
+                                     long long ld_other, float mix,
                                      const int32_t* __restrict__ positions, const int32_t* __restrict__ table_row,
                                      const int32_t* __restrict__ block_table, int table_stride, int page_size, int num_pages,
                                      T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages, int H, int qd, int G,

@@ -1,7 +1,8 @@
 """Grouped-query softmax attention with the options of ``MaskedAttentionSpec``: a norm of every q and k head with one
-scale shared by the heads (or none; before the rotation or after it), rotation by rates (or none), a window that keeps the first tokens visible or a mask of
-chunks, capped scores, a sink per head, a gate per head on the output, and values blended with those of the first
-layer that shares the blend's key.
+scale shared by the heads or without a scale, before the rotation or after it; rotation by rates (or none), whose
+cosine and sine may carry an amplitude; a window that keeps the first tokens visible or a mask of chunks, capped
+scores, a sink per head, a gate per head on the output, and values blended with those of the first layer that shares
+the blend's key.
 
 One merged projection [q | k | v | gate]; one kernel norms, rotates, blends, stores the queries and writes keys and
 values into the layer's pages; then attention over the pages (mask, cap, sink and gate inside the attention kernel)
