@@ -6,9 +6,12 @@
 // as in the reference (crates/prelude-core/src/models/commons/linear.rs:48-77).
 //
 // Each output element is accumulated by one thread over k = 0 .. K-1 in
-// ascending order with fused multiply-adds, so a row's result does not depend
-// on the number of rows, on the row's place in the batch or on the tile it
-// falls in.
+// ascending order with fused multiply-adds, in runs of 16 elements that start
+// at multiples of 16: a run is summed from zero and the runs' sums are added up
+// in ascending order (the rounding of a long sum then grows with the number of
+// runs, not of elements).  The order depends on k alone, so a row's result does
+// not depend on the number of rows, on the row's place in the batch or on the
+// tile it falls in.
 #include "common.cuh"
 
 #define GR_BM 64
@@ -47,6 +50,11 @@ __global__ void __launch_bounds__(256) gemm_ref_kernel(const TA* __restrict__ A,
             Ws[kk][row] = (gn < N && gk < K) ? pb_ld(W + (size_t)gn * ldw + gk) : 0.f;
         }
         __syncthreads();
+        float part[4][4];                                // the sum over this run of 16 elements, from zero
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < GR_BK; ++kk) {
             float a[4], b[4];
@@ -57,8 +65,12 @@ __global__ void __launch_bounds__(256) gemm_ref_kernel(const TA* __restrict__ A,
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
         __syncthreads();
     }
 #pragma unroll

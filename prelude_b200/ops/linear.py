@@ -1,8 +1,8 @@
 """y = x W^T (+ b) with W stored [out, in], in the run's type.
 
 float32: the plain kernel on the float32 units, every output element summed
-in ascending k by one thread; no reduced-precision matrix mode exists on this
-path.
+in ascending k by one thread (in runs of 16 whose sums are then added in
+order); no reduced-precision matrix mode exists on this path.
 
 bfloat16, float32 accumulation:
   * up to 16 rows (decode steps): the weight-streaming kernel of this library
